@@ -1,0 +1,119 @@
+/*
+ * b200fp8 -- C ABI of the B200 (sm_100a) FP8 GEMM library.
+ *
+ * The operation is the one behind the reference project's operator API
+ * (xuezy-mmi/Tensor-Core-FP8, GEMM/include/gemm.cuh:12-55):
+ *
+ *     C[m][n] = sum_k A[m][k] * B[n][k]          "row-col" layout
+ *
+ * A is row-major M x K, B is "column-major K x N", i.e. stored as N rows of K
+ * contiguous elements, both 8-bit floats (e4m3 or e5m2, any of the four
+ * combinations); C is row-major M x N FP32, fully overwritten.  No alpha/beta,
+ * no scaling.  All matrix pointers are DEVICE pointers owned by the caller
+ * unless an entry point says otherwise; calls are asynchronous with respect to
+ * the host and ordered on the given stream, like the reference's launchers
+ * (GEMM/src/gemm.cu:263-277).
+ *
+ * Every function returns a cudaError_t value as int: 0 (cudaSuccess),
+ * 1 (cudaErrorInvalidValue) for bad arguments -- nothing is launched in that
+ * case -- or the CUDA error of the failing runtime call.  Nothing here aborts,
+ * throws or exits.
+ *
+ * Requirements of the tensor-core path: A, B 16-byte aligned, K (and lda, ldb)
+ * multiples of 16.  M and N are arbitrary (ragged edges are clipped in
+ * hardware).  The reference itself needs M, N multiples of 128 and K a
+ * multiple of 64 (GEMM/src/gemm.cu:45-47, :117).
+ */
+#ifndef B200FP8_H
+#define B200FP8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* 8-bit float formats (cuda_fp8.h: __nv_fp8_e4m3 / __nv_fp8_e5m2, typedef'd
+ * e4m3 / e5m2 in GEMM/include/gemm.cuh:6-7). */
+enum { B200FP8_E4M3 = 0, B200FP8_E5M2 = 1 };
+
+/* Kernel selection for b200fp8_options.kernel */
+enum {
+    B200FP8_KERNEL_AUTO = 0,
+    B200FP8_KERNEL_CTA1_N256 = 1, /* one CTA per 128x256 tile                       */
+    B200FP8_KERNEL_CTA1_N128 = 2, /* one CTA per 128x128 tile                       */
+    B200FP8_KERNEL_PAIR_N256 = 3, /* CTA pair (cta_group::2) per 256x256 tile       */
+    B200FP8_KERNEL_SKINNY = 4     /* swap-AB split-K kernel for M <= 128 (HBM-bound) */
+};
+
+typedef struct b200fp8_options {
+    int struct_bytes; /* sizeof(b200fp8_options), for forward compatibility          */
+    int depth;        /* shared-memory ring depth: 2, 4, or 0 = as deep as fits      */
+    int kernel;       /* B200FP8_KERNEL_*                                            */
+    int split_k;      /* skinny kernel: number of K splits, 0 = automatic            */
+    int max_ctas;     /* cap on the persistent grid (0 = one CTA per SM); testing    */
+} b200fp8_options;
+
+/*
+ * Replaces gemm::GEMM (depth = 2) and gemm::GEMM4 (depth = 4), all four dtype
+ * overloads: decl GEMM/include/gemm.cuh:12-55, def GEMM/src/gemm.cu:278-285,
+ * :687-694, :937-944, :1192-1199, :1447-1454, :1479-1548.  Argument order
+ * m, k, n as in the reference; lda = ldb = k, ldc = n.  `stream` is a
+ * cudaStream_t (NULL = the legacy default stream the reference launches on).
+ */
+int b200fp8_gemm_rowcol_f32(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype,
+                            float* c, int depth, void* stream);
+
+/*
+ * Same operation with explicit leading dimensions (in elements) and options.
+ * ldc lets a rank of an N-sharded run write its column block in place inside a
+ * full M x N matrix.  Extends the launchers GEMMex / GEMMex4
+ * (GEMM/src/gemm.cu:263-277, :670-686), which take no options.
+ */
+int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b,
+                               int b_dtype, long long ldb, float* c, long long ldc, const b200fp8_options* options,
+                               void* stream);
+
+/*
+ * The whole call sequence of the reference's benchmark driver for one GEMM
+ * (BmFN, GEMM/gemm_main.cpp:56-64 upload, :77 / :123 operator call, :161
+ * download) with HOST pointers: uploads A and B, runs the operator, downloads
+ * C, and returns when C is complete in host memory.  Device buffers are owned
+ * by the library and reused between calls.  Copies overlap the computation in
+ * column blocks of B / C.  Pinned host memory makes the copies asynchronous.
+ */
+int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_dtype, const void* b_host,
+                                 int b_dtype, float* c_host, int depth);
+
+/*
+ * Seeded synthetic operands: element i (i counted from index_offset) becomes
+ * fp8(sigma * z_i), z_i ~ N(0,1) from a counter-based generator keyed by
+ * (seed, index), cast with round-to-nearest-even and saturate-to-finite -- the
+ * conversion of the FP8 constructors the reference's MakeDenseMatrix uses
+ * (GEMM/include/bm_test_utils.h:131-143); the distribution replaces its
+ * uniform(-1,1).  A shard regenerates its slice from index_offset alone.
+ */
+int b200fp8_fill_normal(void* dst, long long count, int dtype, float sigma, unsigned long long seed,
+                        unsigned long long index_offset, void* stream);
+
+/*
+ * Device status word of the current device: 0 when every kernel of this
+ * library ran its pipeline to completion, otherwise the first recorded code
+ * (a bounded wait inside a kernel ran out).  Synchronises the device.  `reset`
+ * non-zero clears the word after reading.  The reference has no counterpart:
+ * its kernels cannot report anything (GEMM/src/gemm.cu:276 returns only the
+ * launch status).
+ */
+int b200fp8_device_status(int* status, int reset);
+
+/* Number of this library's kernels launched by the calling thread so far. */
+long long b200fp8_launch_count(void);
+
+/* "b200fp8 <version> sm_100a" */
+const char* b200fp8_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200FP8_H */

@@ -1,0 +1,83 @@
+"""ctypes binding of include/b200fp8.h.
+
+The shared library is built in-tree (csrc/Makefile).  There is no fallback: if the
+library is missing, or a call reports a CUDA error, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+E4M3 = 0
+E5M2 = 1
+
+KERNEL_AUTO = 0
+KERNEL_CTA1_N256 = 1
+KERNEL_CTA1_N128 = 2
+KERNEL_PAIR_N256 = 3
+KERNEL_SKINNY = 4
+
+CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
+LIB_PATH = os.path.join(CSRC, "libb200fp8.so")
+CMP_LIB_PATH = os.path.join(CSRC, "libb200fp8_cmp.so")
+
+# every symbol include/b200fp8.h declares
+DECLARED_SYMBOLS = (
+    "b200fp8_gemm_rowcol_f32",
+    "b200fp8_gemm_rowcol_f32_ex",
+    "b200fp8_gemm_rowcol_f32_host",
+    "b200fp8_fill_normal",
+    "b200fp8_device_status",
+    "b200fp8_launch_count",
+    "b200fp8_version",
+)
+# the reference's operator API (GEMM/include/gemm.cuh:12-55) as the C++ linker sees it
+OPERATOR_SYMBOLS = tuple(
+    f"_ZN4gemm{name}EiiiPK13__nv_fp8_{a}{b}Pf"
+    for name in ("4GEMM", "5GEMM4")
+    for a, b in (("e4m3", "S2_"), ("e5m2", "S2_"), ("e4m3", "PK13__nv_fp8_e5m2"), ("e5m2", "PK13__nv_fp8_e4m3"))
+)
+
+
+class Options(ctypes.Structure):
+    _fields_ = [("struct_bytes", ctypes.c_int), ("depth", ctypes.c_int), ("kernel", ctypes.c_int),
+                ("split_k", ctypes.c_int), ("max_ctas", ctypes.c_int)]
+
+
+class B200Fp8Error(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"{what}: CUDA error {code}")
+        self.code = code
+
+
+_lib = None
+
+
+def build(verbose: bool = False) -> None:
+    """Compile the CUDA library for sm_100a (nvcc cross-compiles without a GPU)."""
+    subprocess.check_call(["make", "-C", CSRC, "all"] + ([] if verbose else ["-s"]))
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise FileNotFoundError(f"{LIB_PATH} is not built; run `make -C {CSRC}` (there is no fallback path)")
+        L = ctypes.CDLL(LIB_PATH)
+        vp, ci, ll, ull = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong
+        L.b200fp8_gemm_rowcol_f32.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp]
+        L.b200fp8_gemm_rowcol_f32_ex.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ll,
+                                                 ctypes.POINTER(Options), vp]
+        L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
+        L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]
+        L.b200fp8_device_status.argtypes = [ctypes.POINTER(ci), ci]
+        L.b200fp8_launch_count.restype = ll
+        L.b200fp8_version.restype = ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise B200Fp8Error(code, what)

@@ -1,0 +1,319 @@
+// Host side of the C ABI declared in include/b200fp8.h: argument validation, TMA
+// descriptor encoding, kernel selection and launch.  Replaces the reference's host
+// launchers GEMMex / GEMMex4 (GEMM/src/gemm.cu:263-277, :670-686).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200fp8.h"
+#include "gemm_sm100.cuh"
+#include "gemm_skinny_sm100.cuh"
+#include "fill_fp8.cuh"
+
+namespace b200fp8 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceCtx {
+    bool ready = false;
+    int sm_count = 0;
+    int* status = nullptr;          // device status word
+    // split-K scratch of the skinny kernel (partials + per-tile counters), grown on demand
+    void* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    // buffers of the host-pointer entry point
+    void* host_a = nullptr; size_t host_a_bytes = 0;
+    void* host_b = nullptr; size_t host_b_bytes = 0;
+    void* host_c = nullptr; size_t host_c_bytes = 0;
+    cudaStream_t copy_in = nullptr, compute = nullptr, copy_out = nullptr;
+};
+
+std::mutex g_mutex;
+DeviceCtx g_ctx[kMaxDevices];
+thread_local long long t_launches = 0;
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+
+cudaError_t load_encode() {
+    if (g_encode) return cudaSuccess;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess) return e;
+    if (q != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+    g_encode = reinterpret_cast<EncodeFn>(fn);
+    return cudaSuccess;
+}
+
+cudaError_t get_ctx(DeviceCtx** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceCtx& c = g_ctx[dev];
+    if (!c.ready) {
+        int major = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return e;
+        if (major != 10) return cudaErrorNoKernelImageForDevice;   // sm_100a only: no other path exists
+        if ((e = cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+        if ((e = load_encode()) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&c.status, sizeof(int))) != cudaSuccess) return e;
+        if ((e = cudaMemset(c.status, 0, sizeof(int))) != cudaSuccess) return e;
+        c.ready = true;
+    }
+    *out = &c;
+    return cudaSuccess;
+}
+
+// 2-D tensor map over a row-major matrix of `rows` x `cols` elements with row pitch `ld` elements.
+cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t cols,
+                      uint64_t rows, uint64_t ld, uint32_t box_cols, uint32_t box_rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <int BN, int STAGES, int CTAS>
+cudaError_t launch_main(const DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
+                        long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
+                        cudaStream_t stream) {
+    using L = GemmSmem<BN, STAGES, CTAS>;
+    static bool attr_done[kMaxDevices] = {};
+    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS>;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    GemmArgs args{};
+    args.M = m; args.N = n; args.K = k;
+    args.num_k_blocks = (k + kBlockK - 1) / kBlockK;
+    args.m_tiles = (m + kTileM * CTAS - 1) / (kTileM * CTAS);
+    args.n_tiles = (n + BN - 1) / BN;
+    args.group_m = (CTAS == 2) ? 8 : 16;
+    args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
+    args.tma_store = ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
+    args.C = c; args.ldc = ldc; args.status = ctx.status;
+
+    CUtensorMap ta, tb, tc;
+    cudaError_t e;
+    if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, lda, kBlockK, kTileM)) != cudaSuccess) return e;
+    if ((e = encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows)) != cudaSuccess) return e;
+    if (args.tma_store) {
+        if ((e = encode_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, c, n, m, ldc, 32, 32)) != cudaSuccess) return e;
+    } else {
+        tc = ta;   // unused by the kernel on this path; any valid descriptor
+    }
+
+    const long long tiles = static_cast<long long>(args.m_tiles) * args.n_tiles;
+    int units = ctx.sm_count / CTAS;                     // CTAs (or pairs) resident at once
+    if (max_ctas > 0 && max_ctas / CTAS < units) units = max_ctas / CTAS > 0 ? max_ctas / CTAS : 1;
+    if (tiles < units) units = static_cast<int>(tiles);
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(units * CTAS), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynamicBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, args);
+    if (e == cudaSuccess) ++t_launches;
+    return e;
+}
+
+bool valid_dtype(int d) { return d == B200FP8_E4M3 || d == B200FP8_E5M2; }
+
+cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
+                          long long ldb, float* c, long long ldc, const b200fp8_options* opt, cudaStream_t stream) {
+    if (m < 0 || n < 0 || k < 0 || !valid_dtype(a_dtype) || !valid_dtype(b_dtype)) return cudaErrorInvalidValue;
+    if (m == 0 || n == 0) return cudaSuccess;
+    if (!c || ldc < n) return cudaErrorInvalidValue;
+    if (k == 0) return cudaMemset2DAsync(c, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(n) * 4, m, stream);
+    if (!a || !b || lda < k || ldb < k) return cudaErrorInvalidValue;
+    if ((k % 16) || (lda % 16) || (ldb % 16)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(b) % 16) ||
+        (reinterpret_cast<uintptr_t>(c) % 4))
+        return cudaErrorInvalidValue;
+
+    int depth = opt ? opt->depth : 0;
+    int kernel = opt ? opt->kernel : B200FP8_KERNEL_AUTO;
+    const int split_k = opt ? opt->split_k : 0;
+    const int max_ctas = opt ? opt->max_ctas : 0;
+    if (depth != 0 && depth != 2 && depth != 4) return cudaErrorInvalidValue;
+    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_SKINNY) return cudaErrorInvalidValue;
+    if (split_k < 0 || max_ctas < 0) return cudaErrorInvalidValue;
+
+    DeviceCtx* ctx = nullptr;
+    cudaError_t e = get_ctx(&ctx);
+    if (e != cudaSuccess) return e;
+
+    if (kernel == B200FP8_KERNEL_AUTO) {
+        const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
+        const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
+        if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
+        else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
+        else if (n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
+        else kernel = B200FP8_KERNEL_CTA1_N128;
+    }
+    if (kernel == B200FP8_KERNEL_SKINNY && m > kSkinnyMaxM) return cudaErrorInvalidValue;
+
+#define B200FP8_LAUNCH(BN, ST, CT) \
+    launch_main<BN, ST, CT>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, stream)
+    switch (kernel) {
+        case B200FP8_KERNEL_CTA1_N256:
+            return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);
+        case B200FP8_KERNEL_CTA1_N128:
+            return depth == 2 ? B200FP8_LAUNCH(128, 2, 1) : depth == 4 ? B200FP8_LAUNCH(128, 4, 1) : B200FP8_LAUNCH(128, 6, 1);
+        case B200FP8_KERNEL_PAIR_N256:
+            return depth == 2 ? B200FP8_LAUNCH(256, 2, 2) : depth == 4 ? B200FP8_LAUNCH(256, 4, 2) : B200FP8_LAUNCH(256, 6, 2);
+        case B200FP8_KERNEL_SKINNY: {
+            e = launch_skinny(ctx->sm_count, ctx->status, &ctx->scratch, &ctx->scratch_bytes, g_encode, m, k, n, a, lda,
+                              b, ldb, c, ldc, a_dtype, b_dtype, depth, split_k, stream);
+            if (e == cudaSuccess) ++t_launches;
+            return e;
+        }
+        default:
+            return cudaErrorInvalidValue;
+    }
+#undef B200FP8_LAUNCH
+}
+
+cudaError_t ensure(void** p, size_t* have, size_t want) {
+    if (*have >= want) return cudaSuccess;
+    if (*p) { cudaFree(*p); *p = nullptr; *have = 0; }
+    cudaError_t e = cudaMalloc(p, want);
+    if (e == cudaSuccess) *have = want;
+    return e;
+}
+
+}  // namespace
+}  // namespace b200fp8
+
+using namespace b200fp8;
+
+extern "C" {
+
+int b200fp8_gemm_rowcol_f32(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype, float* c,
+                            int depth, void* stream) {
+    b200fp8_options opt{};
+    opt.struct_bytes = sizeof(opt);
+    opt.depth = depth;
+    return gemm_dispatch(m, k, n, a, a_dtype, k, b, b_dtype, k, c, n, &opt, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b,
+                               int b_dtype, long long ldb, float* c, long long ldc, const b200fp8_options* options,
+                               void* stream) {
+    if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
+    return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, c, ldc, options, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_dtype, const void* b_host, int b_dtype,
+                                 float* c_host, int depth) {
+    if (m < 0 || n < 0 || k < 0) return cudaErrorInvalidValue;
+    if (m == 0 || n == 0) return cudaSuccess;
+    if (!c_host || (k > 0 && (!a_host || !b_host))) return cudaErrorInvalidValue;
+    DeviceCtx* ctx = nullptr;
+    cudaError_t e = get_ctx(&ctx);
+    if (e != cudaSuccess) return e;
+    if (!ctx->compute) {
+        if ((e = cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&ctx->compute, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if ((e = cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking)) != cudaSuccess) return e;
+    }
+    const size_t a_bytes = static_cast<size_t>(m) * k, b_bytes = static_cast<size_t>(n) * k;
+    const size_t c_bytes = static_cast<size_t>(m) * n * sizeof(float);
+    if ((e = ensure(&ctx->host_a, &ctx->host_a_bytes, a_bytes ? a_bytes : 16)) != cudaSuccess) return e;
+    if ((e = ensure(&ctx->host_b, &ctx->host_b_bytes, b_bytes ? b_bytes : 16)) != cudaSuccess) return e;
+    if ((e = ensure(&ctx->host_c, &ctx->host_c_bytes, c_bytes)) != cudaSuccess) return e;
+    float* dc = static_cast<float*>(ctx->host_c);
+    const uint8_t* db = static_cast<const uint8_t*>(ctx->host_b);
+
+    // Column blocks of B / C: upload block j+1 and download block j-1 while block j computes.
+    int blocks = 1;
+    if (static_cast<double>(m) * n * k > 1e11 && n >= 2048) blocks = 8;
+    int nb = ((n + blocks - 1) / blocks + 255) / 256 * 256;
+    if (nb <= 0) nb = n;
+    blocks = (n + nb - 1) / nb;
+    constexpr int kMaxBlocks = 64;
+    if (blocks > kMaxBlocks) return cudaErrorInvalidValue;
+    cudaEvent_t up[kMaxBlocks], done[kMaxBlocks];
+    for (int j = 0; j < blocks; ++j) {
+        cudaEventCreateWithFlags(&up[j], cudaEventDisableTiming);
+        cudaEventCreateWithFlags(&done[j], cudaEventDisableTiming);
+    }
+    b200fp8_options opt{};
+    opt.struct_bytes = sizeof(opt);
+    opt.depth = depth;
+    cudaError_t first = cudaSuccess;
+    auto keep = [&](cudaError_t x) { if (first == cudaSuccess && x != cudaSuccess) first = x; };
+    if (a_bytes) keep(cudaMemcpyAsync(ctx->host_a, a_host, a_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    for (int j = 0; j < blocks && first == cudaSuccess; ++j) {
+        const int n0 = j * nb, nn = (n - n0 < nb) ? n - n0 : nb;
+        if (k) keep(cudaMemcpyAsync(const_cast<uint8_t*>(db) + static_cast<size_t>(n0) * k,
+                                    static_cast<const uint8_t*>(b_host) + static_cast<size_t>(n0) * k,
+                                    static_cast<size_t>(nn) * k, cudaMemcpyHostToDevice, ctx->copy_in));
+        keep(cudaEventRecord(up[j], ctx->copy_in));
+        keep(cudaStreamWaitEvent(ctx->compute, up[j], 0));
+        keep(gemm_dispatch(m, k, nn, ctx->host_a, a_dtype, k, db + static_cast<size_t>(n0) * k, b_dtype, k, dc + n0, n,
+                           &opt, ctx->compute));
+        keep(cudaEventRecord(done[j], ctx->compute));
+        keep(cudaStreamWaitEvent(ctx->copy_out, done[j], 0));
+        keep(cudaMemcpy2DAsync(c_host + n0, static_cast<size_t>(n) * 4, dc + n0, static_cast<size_t>(n) * 4,
+                               static_cast<size_t>(nn) * 4, m, cudaMemcpyDeviceToHost, ctx->copy_out));
+    }
+    keep(cudaStreamSynchronize(ctx->copy_in));
+    keep(cudaStreamSynchronize(ctx->compute));
+    keep(cudaStreamSynchronize(ctx->copy_out));
+    for (int j = 0; j < blocks; ++j) { cudaEventDestroy(up[j]); cudaEventDestroy(done[j]); }
+    return first;
+}
+
+int b200fp8_fill_normal(void* dst, long long count, int dtype, float sigma, unsigned long long seed,
+                        unsigned long long index_offset, void* stream) {
+    if (count < 0 || !valid_dtype(dtype) || (count > 0 && !dst)) return cudaErrorInvalidValue;
+    if (count == 0) return cudaSuccess;
+    DeviceCtx* ctx = nullptr;
+    cudaError_t e = get_ctx(&ctx);
+    if (e != cudaSuccess) return e;
+    e = launch_fill_normal(static_cast<uint8_t*>(dst), count, dtype, sigma, seed, index_offset, ctx->sm_count,
+                           static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) ++t_launches;
+    return e;
+}
+
+int b200fp8_device_status(int* status, int reset) {
+    if (!status) return cudaErrorInvalidValue;
+    DeviceCtx* ctx = nullptr;
+    cudaError_t e = get_ctx(&ctx);
+    if (e != cudaSuccess) return e;
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e;
+    if ((e = cudaMemcpy(status, ctx->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess) return e;
+    if (reset) e = cudaMemset(ctx->status, 0, sizeof(int));
+    return e;
+}
+
+long long b200fp8_launch_count(void) { return t_launches; }
+
+const char* b200fp8_version(void) { return "b200fp8 0.1 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,328 @@
+// Main FP8 GEMM kernel for sm_100a: C[M][N] (FP32, row-major) = A[M][K] * B[N][K]^T with
+// A and B stored as 8-bit floats, K contiguous in both ("row-col" layout of the reference
+// operator gemm::GEMM, GEMM/include/gemm.cuh:12-55).  It replaces the reference's
+// cp.async + mma.sync.m16n8k32 kernels (GEMM/src/gemm.cu:29-262 and its copies).
+//
+// Structure (one persistent CTA, or CTA pair, per SM):
+//   warp 0      TMA producer: A and B k-blocks (128 bytes of K per block, 128-byte swizzle)
+//               into a STAGES-deep shared-memory ring guarded by full/empty mbarriers
+//   warp 1      TMEM allocation; one lane issues tcgen05.mma kind::f8f6f4 (four K=32
+//               instructions per k-block) into one of two TMEM accumulator buffers and
+//               commits to the ring's empty barriers / the accumulator's full barrier
+//   warps 2-5   epilogue: tcgen05.ld 32 rows x 32 columns at a time, stage through swizzled
+//               shared memory, TMA-store 32x32 FP32 boxes (hardware clips ragged M/N edges);
+//               runs concurrently with the next tile's main loop (double-buffered TMEM)
+// CTAS == 2 pairs two CTAs of a cluster on a 256 x BN tile (cta_group::2): each CTA loads
+// its own 128 rows of A and its own half of the B tile (no multicast), the leader CTA
+// issues the MMAs for both, and each CTA drains its own 128 accumulator rows.
+//
+// Every wait on an mbarrier is bounded: after about two seconds the waiting warp records a
+// code in the device status word, raises a CTA-wide abort flag and leaves its loop, so a
+// broken pipeline ends the kernel instead of hanging the GPU.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "ptx_sm100.cuh"
+
+namespace b200fp8 {
+
+struct GemmArgs {
+    int M, N, K;
+    int num_k_blocks;     // ceil(K / 128)
+    int m_tiles;          // tiles along M (tile = 128 * CTAS rows)
+    int n_tiles;          // tiles along N (tile = BN columns)
+    int group_m;          // rasterisation: tiles are walked down `group_m` M-tiles before moving along N
+    uint32_t idesc;       // UMMA instruction descriptor (dtype pair, tile shape)
+    int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
+    float* C;
+    long long ldc;
+    int* status;          // device status word: 0 = ok, else first error code recorded
+};
+
+enum : int {
+    kStatusOk = 0,
+    kStatusProducerTimeout = 101,
+    kStatusMmaTimeout = 102,
+    kStatusEpilogueTimeout = 103,
+    kStatusSkinnyTimeout = 104,
+};
+
+constexpr int kBlockK = 128;         // bytes (= FP8 elements) of K per ring slot: one swizzle-128B row
+constexpr int kTileM = 128;          // accumulator rows per CTA = TMEM lanes
+constexpr int kEpiWarps = 4;
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             bool cluster_scope) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    for (;;) {
+        const bool ok = cluster_scope ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity);
+        if (ok) return true;
+        if ((++spins & 0x3FFu) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = ptx::globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void record_failure(int* status, volatile int* abort_flag, int code) {
+    *abort_flag = 1;
+    if (status) atomicCAS(status, 0, code);
+    __threadfence_block();
+}
+
+template <int BN, int STAGES, int CTAS>
+struct GemmSmem {
+    static constexpr int kABytes = kTileM * kBlockK;
+    static constexpr int kBRows = BN / CTAS;
+    static constexpr int kBBytes = kBRows * kBlockK;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTxBytes = kStageBytes * CTAS;      // bytes landing per ring slot across the pair
+    static constexpr int kEpiBufBytes = 32 * 32 * 4;         // one 32x32 FP32 box
+    static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
+    static constexpr int kRingOff = 0;
+    static constexpr int kEpiOff = STAGES * kStageBytes;
+    static constexpr int kBarOff = kEpiOff + kEpiBytes;      // full[STAGES] empty[STAGES] tfull[2] tempty[2]
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTmemSlotOff = kBarOff + 8 * kNumBars;
+    static constexpr int kAbortOff = kTmemSlotOff + 8;
+    static constexpr int kTotal = kAbortOff + 8;
+    static constexpr int kDynamicBytes = kTotal + 1024;      // slack for manual 1024-byte alignment
+    static constexpr int kTmemCols = 2 * BN;                 // two accumulator buffers (256 or 512: powers of 2)
+};
+
+template <int BN, int STAGES, int CTAS>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                       const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_c,
+                       const GemmArgs args)
+{
+    using L = GemmSmem<BN, STAGES, CTAS>;
+    static_assert(BN % 32 == 0 && BN <= 256 && (BN / CTAS) % 8 == 0, "tile");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+    const bool pair = (CTAS == 2);
+
+    const uint32_t bar_full = smem_base + L::kBarOff;
+    const uint32_t bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    const uint32_t tmem_slot = smem_base + L::kTmemSlotOff;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(bar_tfull + 8 * b, 1);
+            ptx::mbar_init(bar_tempty + 8 * b, kEpiWarps * CTAS);
+        }
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+        ptx::prefetch_tensormap(&tmap_c);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<CTAS>(tmem_slot, L::kTmemCols);
+        ptx::tmem_relinquish<CTAS>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (pair) { ptx::cluster_arrive(); ptx::cluster_wait(); }
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    // persistent tile walk, identical in every role
+    const int num_tiles = args.m_tiles * args.n_tiles;
+    const int first_tile = blockIdx.x / CTAS;
+    const int tile_step = gridDim.x / CTAS;
+    const int nkb = args.num_k_blocks;
+
+    auto tile_coords = [&](int t, int& m0, int& n0) {
+        const int per_group = args.group_m * args.n_tiles;
+        const int g = t / per_group;
+        const int first_m = g * args.group_m;
+        const int gsz = min(args.group_m, args.m_tiles - first_m);
+        const int r = t - g * per_group;
+        const int m_blk = first_m + r % gsz;
+        const int n_blk = r / gsz;
+        m0 = m_blk * (kTileM * CTAS) + static_cast<int>(rank) * kTileM;
+        n0 = n_blk * BN;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        const uint32_t full0 = pair ? ptx::mapa(bar_full, 0) : bar_full;   // the leader's full barriers
+        int s = 0;
+        uint32_t ph = 0;
+        int issued = 0;
+        bool ok = true;
+        for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+            int m0, n0;
+            tile_coords(t, m0, n0);
+            const int nb0 = n0 + static_cast<int>(rank) * L::kBRows;
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, pair)) {
+                    record_failure(args.status, abort_flag, kStatusProducerTimeout);
+                    ok = false;
+                    break;
+                }
+                if (lane == 0) {
+                    const uint32_t a_dst = smem_base + L::kRingOff + s * L::kStageBytes;
+                    const uint32_t b_dst = a_dst + L::kABytes;
+                    if (pair) {
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kTxBytes);
+                        ptx::tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, m0, full0 + 8 * s);
+                        ptx::tma_load_2d_pair(b_dst, &tmap_b, kb * kBlockK, nb0, full0 + 8 * s);
+                    } else {
+                        ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kTxBytes);
+                        ptx::tma_load_2d(a_dst, &tmap_a, kb * kBlockK, m0, bar_full + 8 * s);
+                        ptx::tma_load_2d(b_dst, &tmap_b, kb * kBlockK, nb0, bar_full + 8 * s);
+                    }
+                }
+                __syncwarp();
+                ++issued;
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+        if (!ok && rank == 0) {
+            // leave no copy in flight into this CTA's shared memory: wait (bounded) for the slots armed last
+            const int pending = issued < STAGES ? issued : STAGES;
+            for (int i = 0; i < pending; ++i) {
+                if (s == 0) { s = STAGES; ph ^= 1u; }
+                --s;
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (!ptx::mbar_try_wait(bar_full + 8 * s, ph) && ptx::globaltimer_ns() - t0 < kWaitLimitNs) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (rank == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
+                const int buf = it & 1;
+                const uint32_t aph = (it >> 1) & 1;
+                if (!wait_bounded(bar_tempty + 8 * buf, aph ^ 1u, abort_flag, pair)) {
+                    record_failure(args.status, abort_flag, kStatusMmaTimeout);
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!wait_bounded(bar_full + 8 * s, ph, abort_flag, pair)) {
+                        record_failure(args.status, abort_flag, kStatusMmaTimeout);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t a_src = smem_base + L::kRingOff + s * L::kStageBytes;
+                        const uint64_t adesc = ptx::umma_desc_k128(a_src);
+                        const uint64_t bdesc = ptx::umma_desc_k128(a_src + L::kABytes);
+#pragma unroll
+                        for (int k = 0; k < kBlockK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
+                            ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                        if (pair) ptx::umma_commit_pair(bar_empty + 8 * s, 0x3);
+                        else ptx::umma_commit(bar_empty + 8 * s);
+                    }
+                    __syncwarp();
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok && lane == 0) {
+                    if (pair) ptx::umma_commit_pair(bar_tfull + 8 * buf, 0x3);
+                    else ptx::umma_commit(bar_tfull + 8 * buf);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;                                   // TMEM lane quarter this warp may read
+        const uint32_t stage_base = smem_base + L::kEpiOff + q * (2 * L::kEpiBufBytes);
+        const uint32_t tempty0 = pair ? ptx::mapa(bar_tempty, 0) : bar_tempty;
+        int it = 0;
+        for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+            int m0, n0;
+            tile_coords(t, m0, n0);
+            const int buf = it & 1;
+            const uint32_t aph = (it >> 1) & 1;
+            if (!wait_bounded(bar_tfull + 8 * buf, aph, abort_flag, pair)) {
+                record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
+                break;
+            }
+            ptx::tc_fence_after();
+            const int row0 = m0 + q * 32;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(t_addr + c * 32, v);
+                ptx::tmem_ld_wait();
+                if (c == BN / 32 - 1) {
+                    // accumulator fully read: hand the TMEM buffer back to the MMA warp
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (pair) ptx::mbar_arrive_cluster(tempty0 + 8 * buf);
+                        else ptx::mbar_arrive(bar_tempty + 8 * buf);
+                    }
+                }
+                const int col0 = n0 + c * 32;
+                if (args.tma_store) {
+                    const uint32_t sb = stage_base + (c & 1) * L::kEpiBufBytes;
+                    if (lane == 0) ptx::bulk_wait_group_read<1>();     // the store that last used this buffer has read it
+                    __syncwarp();
+                    const uint32_t row_addr = sb + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        ptx::st_shared_v4(row_addr + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < args.M && col0 < args.N) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        ptx::bulk_commit_group();
+                    }
+                } else {
+                    const int row = row0 + lane;
+                    if (row < args.M) {
+                        float* dst = args.C + static_cast<long long>(row) * args.ldc + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < args.N) dst[j] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+        if (lane == 0) ptx::bulk_wait_group<0>();                 // all stores of this warp are complete
+        __syncwarp();
+    }
+
+    // ---------------- teardown ----------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (pair) { ptx::cluster_arrive(); ptx::cluster_wait(); }
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<CTAS>(tmem_base, L::kTmemCols);
+    }
+}
+
+}  // namespace b200fp8

@@ -1,0 +1,107 @@
+"""Host-side mirror of the reference's operator API for the FP8 GEMM path.
+
+Reference: ``gemm::GEMM`` / ``gemm::GEMM4`` (GEMM/include/gemm.cuh:12-55), called
+by ``BmFN`` (GEMM/gemm_main.cpp:77, :123).  Same names, same argument order
+``(m, k, n, a, b, out)``, same layouts: ``a`` is row-major M x K, ``b`` is
+"column-major K x N" = N rows of K elements, ``out`` is row-major M x N FP32.  The dtype
+pair is taken from the tensors (``torch.float8_e4m3fn`` / ``torch.float8_e5m2``), which
+is what the C++ overload set does with the pointer types.
+
+torch is used only for device memory and streams; the computation is the CUDA library
+behind include/b200fp8.h.  Errors surface as ``B200Fp8Error`` carrying the cudaError_t
+value the reference's functions would have returned.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _cabi
+from ._cabi import (E4M3, E5M2, KERNEL_AUTO, KERNEL_CTA1_N128, KERNEL_CTA1_N256, KERNEL_PAIR_N256,  # noqa: F401
+                    KERNEL_SKINNY, B200Fp8Error, Options)
+
+_DTYPES = {torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"expected float8_e4m3fn or float8_e5m2, got {t.dtype}") from None
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _gemm(m, k, n, a, b, out, depth, kernel=KERNEL_AUTO, split_k=0, max_ctas=0, lda=None, ldb=None, ldc=None):
+    if not (a.is_cuda and b.is_cuda and out.is_cuda):
+        raise ValueError("a, b and out must be CUDA tensors (device pointers, as in the reference)")
+    if out.dtype != torch.float32:
+        raise TypeError("out must be float32")
+    opt = Options(ctypes.sizeof(Options), depth, kernel, split_k, max_ctas)
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().b200fp8_gemm_rowcol_f32_ex(
+            m, k, n, a.data_ptr(), dtype_code(a), k if lda is None else lda, b.data_ptr(), dtype_code(b),
+            k if ldb is None else ldb, out.data_ptr(), n if ldc is None else ldc, ctypes.byref(opt),
+            _stream_ptr(out.device))
+    _cabi.check(rc, f"GEMM m={m} k={k} n={n}")
+    return out
+
+
+def GEMM(m: int, k: int, n: int, a_matrix: torch.Tensor, b_matrix: torch.Tensor, output_matrix: torch.Tensor):
+    """``gemm::GEMM`` (GEMM/include/gemm.cuh:12-15 and its three dtype overloads): the "2-stage" entry."""
+    return _gemm(m, k, n, a_matrix, b_matrix, output_matrix, depth=2)
+
+
+def GEMM4(m: int, k: int, n: int, a_matrix: torch.Tensor, b_matrix: torch.Tensor, output_matrix: torch.Tensor):
+    """``gemm::GEMM4`` (GEMM/include/gemm.cuh:18-21 and overloads): the "4-stage" entry."""
+    return _gemm(m, k, n, a_matrix, b_matrix, output_matrix, depth=4)
+
+
+def gemm_ex(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, depth: int = 0,
+            kernel: int = KERNEL_AUTO, split_k: int = 0, max_ctas: int = 0, ldc: int | None = None):
+    """Extended form: shapes from the tensors (a: [M, K], b: [N, K]); ring depth 0 = as deep as fits."""
+    m, k = a.shape
+    n, k2 = b.shape
+    if k != k2:
+        raise ValueError("a and b disagree on K")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    return _gemm(m, k, n, a, b, out, depth, kernel, split_k, max_ctas, a.stride(0) if m > 1 else k,
+                 b.stride(0) if n > 1 else k, ldc if ldc is not None else (out.stride(0) if m > 1 else n))
+
+
+def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, depth: int = 0):
+    """BmFN's whole sequence with HOST tensors (GEMM/gemm_main.cpp:56-64, :77, :161): upload, run, download."""
+    if a.is_cuda or b.is_cuda or out.is_cuda:
+        raise ValueError("gemm_host takes host tensors")
+    m, k = a.shape
+    n, _ = b.shape
+    rc = _cabi.lib().b200fp8_gemm_rowcol_f32_host(m, k, n, a.data_ptr(), dtype_code(a), b.data_ptr(), dtype_code(b),
+                                                   out.data_ptr(), depth)
+    _cabi.check(rc, f"gemm_host m={m} k={k} n={n}")
+    return out
+
+
+def fill_normal(t: torch.Tensor, sigma: float, seed: int, index_offset: int = 0):
+    """Seeded synthetic operand: t[i] = fp8(sigma * N(0,1)), RNE + saturate-to-finite, keyed by (seed, index)."""
+    if not t.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    with torch.cuda.device(t.device):
+        rc = _cabi.lib().b200fp8_fill_normal(t.data_ptr(), t.numel(), dtype_code(t), float(sigma), int(seed),
+                                              int(index_offset), _stream_ptr(t.device))
+    _cabi.check(rc, "fill_normal")
+    return t
+
+
+def device_status(reset: bool = True) -> int:
+    """0 unless a bounded wait inside one of the kernels ran out on the current device."""
+    st = ctypes.c_int(-1)
+    _cabi.check(_cabi.lib().b200fp8_device_status(ctypes.byref(st), 1 if reset else 0), "device_status")
+    return st.value
+
+
+def launch_count() -> int:
+    return int(_cabi.lib().b200fp8_launch_count())
