@@ -1,0 +1,409 @@
+"""Benchmark of the FP8 GEMM path (one JSON line on stdout, printed by rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workloads (synthetic operands, N(0,1) cast to e4m3 with RNE + saturate-to-finite, seeded):
+    shard32768  M = N = K = 32768, B and C column-split evenly over the N GPUs, A replicated
+                (default; total work fixed => "strong" scaling; no collective in the timed step)
+    gemm8192    M = N = K = 8192 on every GPU (replicas)
+    gemm4096    M = N = K = 4096
+    ffn_up      M = 8192, K = 8192, N = 28672
+    ffn_down    M = 8192, K = 28672, N = 8192
+    skinny16    M = 16, N = K = 8192 (HBM-bound; rotates over distinct B buffers so each step streams from HBM)
+
+A step is one operator call on operands resident in HBM.  `value` is whole-job TFLOPS over all
+GPUs from the max-over-ranks device time; `e2e` is the same quantity through the host-pointer
+entry point (pinned host buffers, uploads and the download of C inside the timed region).
+`--impl reference` times the reference's own CPU implementation of the path (its verification
+loop, GEMM/gemm_main.cpp:45-52, as restated by the oracle) on all host threads over a bounded
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (M, K, N, sharded)
+    "shard32768": (32768, 32768, 32768, True),
+    "gemm8192": (8192, 8192, 8192, False),
+    "gemm4096": (4096, 4096, 4096, False),
+    "ffn_up": (8192, 8192, 28672, False),
+    "ffn_down": (8192, 28672, 8192, False),
+    "skinny16": (16, 8192, 8192, False),
+}
+SEED_BASE = 0xB200F800
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_burst": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksThrottleReasonHwPowerBrakeSlowdown: "hw_power_brake",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+def cpu_reference_rate(M, K, N, rows_per_thread: int, seed_a: int, seed_b: int):
+    """The reference's CPU loop (oracle port) on a bounded sample: returns (TFLOPS, threads, description, seconds)."""
+    import numpy as np
+    from oracle import fp8_oracle as fo
+    threads = fo.max_threads()
+    rows = min(M, rows_per_thread * threads)
+    cols = min(N, 256)
+    A = fo.fill_normal(rows * K, fo.E4M3, 1.0, seed_a).reshape(rows, K)
+    B = fo.fill_normal(cols * K, fo.E4M3, 1.0, seed_b).reshape(cols, K)
+    t0 = time.perf_counter()
+    C = fo.gemm_ref_float(A, fo.E4M3, B, fo.E4M3, threads=threads)
+    dt = time.perf_counter() - t0
+    assert np.isfinite(C).all()
+    flops = 2.0 * rows * cols * K
+    return flops / dt / 1e12, threads, f"rows 0..{rows - 1} x cols 0..{cols - 1} of C at full K={K} ({flops / 1e9:.2f} GFLOP)", dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    M, K, N, sharded = WORKLOADS[args.workload]
+    # bounded sample per step: about a second of work per step on all host threads
+    rates = []
+    for i in range(args.warmup + args.steps):
+        r, threads, sample, dt = cpu_reference_rate(M, K, N, 8, SEED_BASE + 64, SEED_BASE + 65)
+        if i >= args.warmup:
+            rates.append((r, dt))
+    total_t = sum(d for _, d in rates)
+    value = sum(r * d for r, d in rates) / total_t
+    line = {
+        "impl": "reference", "metric": "fp8_gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_t / len(rates),
+        "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "fp8",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "layout": "row-col", "a": "e4m3", "b": "e4m3",
+                   "out": "f32"},
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port",
+                         "sample": "each step: " + sample + "; the reference's float loop "
+                                   "(GEMM/gemm_main.cpp:45-52) restated in oracle/fp8_oracle.c, OpenMP over rows"},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="shard32768", choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the cuBLASLt / 8192^3 side measurements")
+    ap.add_argument("--allgather", action="store_true", help="also time an NCCL all-gather of the C shards (N > 1)")
+    ap.add_argument("--kernel", type=int, default=0)
+    ap.add_argument("--depth", type=int, default=0)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    g = pkg.gemm
+    shard_mod = pkg.shard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    M, K, N, sharded = WORKLOADS[args.workload]
+    sh = shard_mod.column_shard(N, rank, world) if sharded else shard_mod.Shard(rank, world, 0, N)
+    n_local = sh.n
+    seed_a, seed_b = SEED_BASE + 64, SEED_BASE + 65
+    f8 = torch.float8_e4m3fn
+
+    # operands: several B (and C) buffers for small workloads so that every step reads from HBM, not L2
+    bytes_per_set = n_local * K + 4 * M * n_local
+    nsets = 1 if (M * K + bytes_per_set) > (512 << 20) else max(2, min(8, (1 << 30) // max(1, bytes_per_set)))
+    a = torch.empty((M, K), dtype=f8, device=dev)
+    g.fill_normal(a, 1.0, seed_a)
+    bs, cs = [], []
+    for i in range(nsets):
+        b = torch.empty((n_local, K), dtype=f8, device=dev)
+        g.fill_normal(b, 1.0, seed_b + 1000 * i, index_offset=sh.n_begin * K)
+        bs.append(b)
+        cs.append(torch.empty((M, n_local), dtype=torch.float32, device=dev))
+    torch.cuda.synchronize()
+
+    def step(i):
+        g.gemm_ex(a, bs[i % nsets], cs[i % nsets], depth=args.depth, kernel=args.kernel)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    launches0 = g.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(physical_gpu_index(local_rank)) as clk:
+        ev[0].record()
+        for i in range(args.steps):
+            step(i)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+    launches = g.launch_count() - launches0
+    barrier()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    if g.device_status() != 0:
+        raise SystemExit("device status word is non-zero: a kernel's bounded wait ran out")
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    max_ms = float(t.item())
+    ms_per_step = max_ms / args.steps
+
+    replicas = 1 if sharded else world
+    flops_job = 2.0 * M * K * N * replicas                      # per step, all ranks together
+    value = flops_job / (ms_per_step * 1e-3) / 1e12
+
+    # roofline of the dominant kernel on this rank
+    peaks = measured_peaks()
+    flops_launch = 2.0 * M * K * n_local
+    bytes_launch = float(M * K + n_local * K + 4 * M * n_local)
+    avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
+    hbm_bound = M <= 128
+    if hbm_bound:
+        ach = bytes_launch / (avg_launch_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (copy bandwidth)",
+                "frac_of_nominal_8TBs": ach / NOMINAL_HBM_GBS}
+    else:
+        ach = flops_launch / (avg_launch_ms * 1e-3) / 1e12
+        peak = 2.0 * peaks["bf16_sustained"]
+        roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "peak_source": peaks["source"] + ": 2 x sustained cuBLAS bf16 (fp8 issues at twice the bf16 rate)",
+                "frac_of_burst_peak": ach / (2.0 * peaks["bf16_burst"]),
+                "frac_of_nominal_4500": ach / NOMINAL_FP8_TFLOPS}
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+    roof["algorithmic_bytes"] = bytes_launch
+    roof["algorithmic_flops"] = flops_launch
+    roof["kernel_ms"] = avg_launch_ms
+
+    line = {
+        "metric": "fp8_gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "n_per_rank": n_local, "layout": "row-col",
+                   "a": "e4m3", "b": "e4m3", "out": "f32", "parallelism": f"n-shard x{world}" if sharded else f"replicas x{world}",
+                   "l2": "inputs larger than L2" if nsets == 1 else f"rotating over {nsets} distinct B/C buffer sets larger than L2",
+                   "kernel": args.kernel, "depth": args.depth},
+        "roofline": roof, "gpu_launches": int(launches), "clocks": clk.summary(),
+        "pct_of_nominal_fp8_peak": 100.0 * value / (NOMINAL_FP8_TFLOPS * world),
+    }
+
+    # ---- end to end through the host-pointer entry point (pinned host buffers) ----
+    if not args.no_e2e:
+        ha = torch.empty((M, K), dtype=torch.uint8).pin_memory().view(f8)
+        hb = torch.empty((n_local, K), dtype=torch.uint8).pin_memory().view(f8)
+        hc = torch.empty((M, n_local), dtype=torch.float32).pin_memory()
+        ha.view(torch.uint8).copy_(a.view(torch.uint8))
+        hb.view(torch.uint8).copy_(bs[0].view(torch.uint8))
+        g.gemm_host(ha, hb, hc, depth=args.depth)               # warm-up: allocates the library's device buffers
+        barrier()
+        t0 = time.perf_counter()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            g.gemm_host(ha, hb, hc, depth=args.depth)
+        e2e_ms = (time.perf_counter() - t0) * 1e3               # the call returns when C is in host memory
+        tt = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item()) / args.e2e_steps
+        line["e2e"] = {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                       "h2d_bytes_per_step": int(M * K + n_local * K), "d2h_bytes_per_step": int(4 * M * n_local),
+                       "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+                       "api": "b200fp8_gemm_rowcol_f32_host (upload A, B; operator; download C), wall clock, max over ranks"}
+        del ha, hb, hc
+
+    # ---- optional NCCL all-gather of the C shards, timed separately ----
+    if args.allgather and world > 1 and sharded:
+        full = torch.empty((world, M, n_local), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(full, cs[0])
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.all_gather_into_tensor(full, cs[0])
+        e1.record()
+        torch.cuda.synchronize()
+        tg = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        line["allgather"] = {"ms": float(tg.item()), "bytes_received_per_rank": int(4 * M * n_local * (world - 1)),
+                             "layout": "[rank][M][N/R] blocks"}
+        del full
+
+    # ---- side measurements on rank 0 at N = 1: the 8192^3 target shape and cuBLASLt on the same buffers ----
+    if rank == 0 and world == 1 and not args.no_extras:
+        extras = {}
+        cmp_path = pkg._cabi.CMP_LIB_PATH
+        cmp = ctypes.CDLL(cmp_path) if os.path.exists(cmp_path) else None
+        if cmp is not None:
+            cmp.b200fp8_cmp_cublaslt.argtypes = [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                                                      ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                                      ctypes.c_int, ctypes.c_int,
+                                                                      ctypes.POINTER(ctypes.c_float),
+                                                                      ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
+        for name in ("gemm8192", args.workload):
+            if name in extras:
+                continue
+            m2, k2, n2, _ = WORKLOADS[name]
+            if name == args.workload:
+                a2, b2, c2 = a, bs[0], cs[0]
+            else:
+                a2 = torch.empty((m2, k2), dtype=f8, device=dev)
+                b2 = torch.empty((n2, k2), dtype=f8, device=dev)
+                c2 = torch.empty((m2, n2), dtype=torch.float32, device=dev)
+                g.fill_normal(a2, 1.0, seed_a + 7)
+                g.fill_normal(b2, 1.0, seed_b + 7)
+            iters = 10 if 2.0 * m2 * k2 * n2 < 5e12 else 3
+            for _ in range(3):
+                g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+            e1.record()
+            torch.cuda.synchronize()
+            ours_ms = e0.elapsed_time(e1) / iters
+            entry = {"ms": ours_ms, "tflops": 2.0 * m2 * k2 * n2 / ours_ms / 1e9}
+            if cmp is not None:
+                best = None
+                for fast in (0, 1):
+                    ms = ctypes.c_float(-1)
+                    found = ctypes.c_int(0)
+                    rc = cmp.b200fp8_cmp_cublaslt(m2, k2, n2, a2.data_ptr(), 0, b2.data_ptr(), 0, c2.data_ptr(), iters, 8,
+                                                  fast, ctypes.byref(ms), ctypes.byref(found),
+                                                  torch.cuda.current_stream().cuda_stream)
+                    if rc == 0 and (best is None or ms.value < best):
+                        best = ms.value
+                if best:
+                    entry["cublaslt_ms"] = best
+                    entry["cublaslt_tflops"] = 2.0 * m2 * k2 * n2 / best / 1e9
+                    entry["vs_cublaslt"] = best / ours_ms
+            extras[name] = entry
+        line["side"] = extras
+
+    # ---- the reference's CPU loop timed on this box's host cores (rank 0, N = 1 only) ----
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r, threads, sample, dt = cpu_reference_rate(M, K, N, 64, seed_a, seed_b)
+        line["cpu_baseline"] = {"value": r, "unit": "TFLOPS", "cores": threads, "kind": "port",
+                                "sample": sample + f", {dt:.1f} s; the reference's float loop "
+                                "(GEMM/gemm_main.cpp:45-52) restated in oracle/fp8_oracle.c, OpenMP over rows"}
+
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -22,9 +22,6 @@ struct DeviceCtx {
     bool ready = false;
     int sm_count = 0;
     int* status = nullptr;          // device status word
-    // split-K scratch of the skinny kernel (partials + per-tile counters), grown on demand
-    void* scratch = nullptr;
-    size_t scratch_bytes = 0;
     // buffers of the host-pointer entry point
     void* host_a = nullptr; size_t host_a_bytes = 0;
     void* host_b = nullptr; size_t host_b_bytes = 0;
@@ -186,8 +183,8 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         case B200FP8_KERNEL_PAIR_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 2) : depth == 4 ? B200FP8_LAUNCH(256, 4, 2) : B200FP8_LAUNCH(256, 6, 2);
         case B200FP8_KERNEL_SKINNY: {
-            e = launch_skinny(ctx->sm_count, ctx->status, &ctx->scratch, &ctx->scratch_bytes, g_encode, m, k, n, a, lda,
-                              b, ldb, c, ldc, a_dtype, b_dtype, depth, split_k, stream);
+            e = launch_skinny(ctx->sm_count, ctx->status, g_encode, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
+                              depth, split_k, stream);
             if (e == cudaSuccess) ++t_launches;
             return e;
         }

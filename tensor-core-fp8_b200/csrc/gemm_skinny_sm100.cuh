@@ -5,10 +5,12 @@
 //   * swap-AB: a CTA owns 128 rows of B (N rides the 128-lane UMMA M axis) and all of A's
 //     rows padded to MP in {16,32,64,128} (the UMMA N axis; TMA zero-fills the padding),
 //     so the accumulator is C^T: TMEM lane = n, column = m;
-//   * split-K: grid = (N tiles) x (K splits); every CTA streams its K range through a deep
-//     TMA ring; with more than one split the partial tiles go to scratch memory and the
-//     LAST CTA to finish a tile (a counter per tile, no spinning) adds the partials in
-//     split order -- the result does not depend on which CTA was last;
+//   * split-K inside a thread-block cluster: grid = (N tiles) x (K splits), the `splits`
+//     CTAs of one N tile form a cluster (1 x splits x 1).  Every CTA streams its K range
+//     through a deep TMA ring; the partial tiles are then parked in each CTA's own shared
+//     memory and reduce-scattered through distributed shared memory: CTA r adds rows
+//     r*rows_per.. of all partials in split order and writes them to C.  No scratch memory
+//     in HBM, no atomics, and the result does not depend on timing;
 //   * two CTAs fit per SM, so one CTA's epilogue overlaps the other's stream.
 //
 // Same operator contract as the main kernel (reference: gemm::GEMM, GEMM/include/gemm.cuh:12-55;
@@ -24,18 +26,18 @@ namespace b200fp8 {
 constexpr int kSkinnyMaxM = 128;
 constexpr int kSkinnyTileN = 128;
 constexpr int kSkinnyThreads = 192;
+constexpr int kSkinnyMaxSplits = 8;      // portable cluster size
 
 struct SkinnyArgs {
     int M, N, K;
     int kb_total;        // ceil(K / 128)
     int kb_per_split;    // k-blocks per split (last split may be shorter, never empty)
-    int splits;
+    int splits;          // = cluster size along y
     int stages;
+    int vec_store;       // 1: C rows are 16-byte aligned (ldc % 4 == 0 and C % 16 == 0)
     uint32_t idesc;
     float* C;
     long long ldc;
-    float* partial;      // [splits][M][N] FP32, used when splits > 1
-    unsigned int* counters;  // [n_tiles], zero between launches
     int* status;
 };
 
@@ -46,9 +48,17 @@ struct SkinnySmem {
     static constexpr int kStageBytes = kBBytes + kABytes;
     static constexpr int kMaxStages = 8;
     static constexpr int kTmemCols = MP < 32 ? 32 : MP;
+    static constexpr int kPartialBytes = MP * kSkinnyTileN * 4;   // parked partial tile [m][n]; fits in two ring slots
     __host__ __device__ static constexpr int bar_off(int stages) { return stages * kStageBytes; }
     __host__ __device__ static constexpr int dynamic_bytes(int stages) { return stages * kStageBytes + 8 * (2 * kMaxStages + 1) + 32 + 1024; }
 };
+
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr) : "memory");
+    return v;
+}
 
 template <int MP>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
@@ -63,6 +73,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     const int stages = args.stages;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const bool clustered = args.splits > 1;
 
     const uint32_t bar_full = smem_base + L::bar_off(stages);
     const uint32_t bar_empty = bar_full + 8 * L::kMaxStages;
@@ -71,11 +82,9 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     const uint32_t tmem_slot = smem_base + misc_off;
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
-    volatile unsigned int* last_flag = reinterpret_cast<volatile unsigned int*>(smem_gen + misc_off + 16);
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        *last_flag = 0;
         for (int s = 0; s < stages; ++s) {
             ptx::mbar_init(bar_full + 8 * s, 1);
             ptx::mbar_init(bar_empty + 8 * s, 1);
@@ -95,7 +104,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     const uint32_t tmem_base = *tmem_slot_gen;
 
     const int n_tile = blockIdx.x;
-    const int split = blockIdx.y;
+    const int split = blockIdx.y;                  // = rank in the cluster (1 x splits x 1)
     const int n0 = n_tile * kSkinnyTileN;
     const int kb0 = split * args.kb_per_split;
     const int kb1 = min(args.kb_total, kb0 + args.kb_per_split);
@@ -157,55 +166,73 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         __syncwarp();
     } else {
         // ---------------- epilogue: 128 threads, thread = one column n of C ----------------
+        // bar_acc completes after every MMA of this CTA has finished, i.e. after the ring's
+        // shared memory was last read and long after it was last written: it is free to reuse.
         const int q = warp & 3;
-        const int n = n0 + q * 32 + lane;
-        const bool n_ok = n < args.N;
+        const int n_local = q * 32 + lane;
+        const int n = n0 + n_local;
         bool ok = wait_bounded(bar_acc, 0, abort_flag, false);
         if (!ok) record_failure(args.status, abort_flag, kStatusSkinnyTimeout);
         __syncwarp();
         ptx::tc_fence_after();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        const bool direct = (args.splits == 1);
-        float* out = direct ? args.C : args.partial + static_cast<long long>(split) * args.M * args.N;
-        const long long ld = direct ? args.ldc : args.N;
         if (ok) {
+            float* park = reinterpret_cast<float*>(smem_gen);      // [m][128] partial tile
 #pragma unroll
             for (int c = 0; c < MP / 16; ++c) {
-                uint32_t v[16];
-                ptx::tmem_ld_32x16(t_addr + c * 16, v);
-                ptx::tmem_ld_wait();
-                if (n_ok) {
+                if (c * 16 < args.M) {
+                    uint32_t v[16];
+                    ptx::tmem_ld_32x16(t_addr + c * 16, v);
+                    ptx::tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = c * 16 + j;
-                        if (m < args.M) out[m * ld + n] = __uint_as_float(v[j]);   // a warp writes 128 contiguous bytes
+                        if (m < args.M) {
+                            if (clustered) park[m * kSkinnyTileN + n_local] = __uint_as_float(v[j]);
+                            else if (n < args.N) args.C[m * args.ldc + n] = __uint_as_float(v[j]);   // 128 contiguous bytes per warp
+                        }
                     }
                 }
             }
         }
-        if (!direct) {
-            // publish this split's partial tile, then find out whether this CTA is the last of the tile
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (warp == 2 && lane == 0) {
-                const unsigned int prev = atomicAdd(args.counters + n_tile, 1u);
-                *last_flag = (prev == static_cast<unsigned int>(args.splits - 1)) ? 1u : 0u;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*last_flag) {
-                __threadfence();
-                if (n_ok) {
-                    for (int m = 0; m < args.M; ++m) {
-                        float acc = 0.0f;
-                        const float* p = args.partial + static_cast<long long>(m) * args.N + n;
-                        for (int s = 0; s < args.splits; ++s)
-                            acc += __ldcg(p + static_cast<long long>(s) * args.M * args.N);
-                        args.C[m * args.ldc + n] = acc;
-                    }
+    }
+
+    if (clustered) {
+        // ---------------- reduce-scatter across the cluster through distributed shared memory ----------------
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+        const int rows_per = (args.M + args.splits - 1) / args.splits;
+        const int m_begin = split * rows_per;
+        const int m_end = min(args.M, m_begin + rows_per);
+        const int items = max(0, m_end - m_begin) * (kSkinnyTileN / 4);      // float4 groups
+        if (*abort_flag == 0) {
+            for (int i = threadIdx.x; i < items; i += kSkinnyThreads) {
+                const int m = m_begin + i / (kSkinnyTileN / 4);
+                const int cg = i % (kSkinnyTileN / 4);
+                const uint32_t local = smem_base + static_cast<uint32_t>((m * kSkinnyTileN + cg * 4) * 4);
+                float4 part[kSkinnyMaxSplits];
+#pragma unroll
+                for (int s = 0; s < kSkinnyMaxSplits; ++s)
+                    if (s < args.splits) part[s] = ld_cluster_f4(ptx::mapa(local, s));
+                float4 acc = part[0];
+#pragma unroll
+                for (int s = 1; s < kSkinnyMaxSplits; ++s)
+                    if (s < args.splits) { acc.x += part[s].x; acc.y += part[s].y; acc.z += part[s].z; acc.w += part[s].w; }
+                const int n = n0 + cg * 4;
+                float* dst = args.C + m * args.ldc + n;
+                if (args.vec_store && n + 3 < args.N) {
+                    *reinterpret_cast<float4*>(dst) = acc;
+                } else {
+                    if (n < args.N) dst[0] = acc.x;
+                    if (n + 1 < args.N) dst[1] = acc.y;
+                    if (n + 2 < args.N) dst[2] = acc.z;
+                    if (n + 3 < args.N) dst[3] = acc.w;
                 }
-                if (warp == 2 && lane == 0) args.counters[n_tile] = 0;   // ready for the next launch
             }
         }
+        // peers may still be reading this CTA's shared memory
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
     }
 
     ptx::tc_fence_before();
@@ -241,8 +268,8 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
     if (s <= 0) {
         s = (2 * sm_count) / n_tiles;
         if (s < 1) s = 1;
-        if (s > 16) s = 16;
     }
+    if (s > kSkinnyMaxSplits) s = kSkinnyMaxSplits;
     if (s > kb_total) s = kb_total;
     int per = (kb_total + s - 1) / s;
     s = (kb_total + per - 1) / per;          // no empty split
@@ -256,16 +283,6 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
         if (st < 2) st = 2;
     }
     *stages = st;
-}
-
-// Scratch layout: a fixed 64 KiB block of per-tile counters (zero between launches), then the
-// partial tiles [splits][M][N].  The fixed block keeps counters and partials apart whatever N is.
-constexpr size_t kSkinnyCounterBytes = 64 * 1024;
-constexpr int kSkinnyMaxTiles = static_cast<int>(kSkinnyCounterBytes / sizeof(unsigned int));
-
-inline size_t skinny_scratch_bytes(int m, int n, int splits) {
-    const size_t partial = splits > 1 ? static_cast<size_t>(splits) * m * n * sizeof(float) : 0;
-    return kSkinnyCounterBytes + partial;
 }
 
 template <int MP>
@@ -282,29 +299,34 @@ cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const
         if (e != cudaSuccess) return e;
         attr_bytes[dev] = bytes;
     }
-    kernel<<<dim3(n_tiles, args.splits, 1), kSkinnyThreads, bytes, stream>>>(tb, ta, args);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(n_tiles), static_cast<unsigned>(args.splits), 1);
+    cfg.blockDim = dim3(kSkinnyThreads, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(bytes);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(args.splits);
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, tb, ta, args);
 }
 
-// Launches the skinny kernel with caller-provided scratch (counters first, partials after).
-inline cudaError_t launch_skinny_with_scratch(int sm_count, int* status, void* scratch, SkinnyEncodeFn enc, int m, int k,
-                                              int n, const void* a, long long lda, const void* b, long long ldb, float* c,
-                                              long long ldc, int a_dtype, int b_dtype, int splits, int kb_per_split,
-                                              int stages, cudaStream_t stream) {
-    (void)sm_count;
+inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, int m, int k, int n, const void* a,
+                                 long long lda, const void* b, long long ldb, float* c, long long ldc, int a_dtype,
+                                 int b_dtype, int depth, int split_k, cudaStream_t stream) {
     const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
     const int n_tiles = (n + kSkinnyTileN - 1) / kSkinnyTileN;
+    if (n_tiles > 65535 * 32) return cudaErrorInvalidValue;
     SkinnyArgs args{};
+    skinny_plan(sm_count, n, k, mp, depth, split_k, &args.splits, &args.kb_per_split, &args.stages);
     args.M = m; args.N = n; args.K = k;
     args.kb_total = (k + kBlockK - 1) / kBlockK;
-    args.kb_per_split = kb_per_split;
-    args.splits = splits;
-    args.stages = stages;
+    args.vec_store = ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
     args.idesc = make_idesc_f8(b_dtype, a_dtype, 128, mp);   // swapped: B feeds the UMMA A operand
     args.C = c; args.ldc = ldc;
-    if (n_tiles > kSkinnyMaxTiles) return cudaErrorInvalidValue;
-    args.counters = static_cast<unsigned int*>(scratch);
-    args.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + kSkinnyCounterBytes);
     args.status = status;
     CUtensorMap tb, ta;
     cudaError_t e;
@@ -316,25 +338,6 @@ inline cudaError_t launch_skinny_with_scratch(int sm_count, int* status, void* s
         case 64: return launch_skinny_mp<64>(tb, ta, args, n_tiles, stream);
         default: return launch_skinny_mp<128>(tb, ta, args, n_tiles, stream);
     }
-}
-
-// Library-owned scratch, grown on demand (counters must start at zero; the kernel re-zeroes them).
-inline cudaError_t launch_skinny(int sm_count, int* status, void** scratch, size_t* scratch_bytes, SkinnyEncodeFn enc,
-                                 int m, int k, int n, const void* a, long long lda, const void* b, long long ldb, float* c,
-                                 long long ldc, int a_dtype, int b_dtype, int depth, int split_k, cudaStream_t stream) {
-    const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
-    int splits, per, stages;
-    skinny_plan(sm_count, n, k, mp, depth, split_k, &splits, &per, &stages);
-    const size_t need = skinny_scratch_bytes(m, n, splits);
-    if (*scratch_bytes < need) {
-        if (*scratch) { cudaFree(*scratch); *scratch = nullptr; *scratch_bytes = 0; }   // cudaFree waits for running kernels
-        cudaError_t e = cudaMalloc(scratch, need);
-        if (e != cudaSuccess) return e;
-        if ((e = cudaMemset(*scratch, 0, need)) != cudaSuccess) return e;
-        *scratch_bytes = need;
-    }
-    return launch_skinny_with_scratch(sm_count, status, *scratch, enc, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
-                                      splits, per, stages, stream);
 }
 
 }  // namespace b200fp8
