@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -17,11 +18,14 @@ namespace b200fp8 {
 namespace {
 
 constexpr int kMaxDevices = 64;
+constexpr int kPaceSlots = 256;
 
 struct DeviceCtx {
     bool ready = false;
     int sm_count = 0;
     int* status = nullptr;          // device status word
+    unsigned int* pace = nullptr;   // ring of tile-pacing counters, one per launch in flight
+    unsigned int pace_next = 0;
     // buffers of the host-pointer entry point
     void* host_a = nullptr; size_t host_a_bytes = 0;
     void* host_b = nullptr; size_t host_b_bytes = 0;
@@ -64,6 +68,7 @@ cudaError_t get_ctx(DeviceCtx** out) {
         if ((e = load_encode()) != cudaSuccess) return e;
         if ((e = cudaMalloc(&c.status, sizeof(int))) != cudaSuccess) return e;
         if ((e = cudaMemset(c.status, 0, sizeof(int))) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&c.pace, kPaceSlots * sizeof(unsigned int))) != cudaSuccess) return e;
         c.ready = true;
     }
     *out = &c;
@@ -83,13 +88,33 @@ cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int BN, int STAGES, int CTAS>
-cudaError_t launch_main(const DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
+// Tuning knobs read once from the environment (B200FP8_*); defaults are the measured best.
+struct Tune {
+    int wait_hint_ns = 0;
+    int group_m_pair = 16;
+    int group_m_single = 16;
+    int debug = 0;
+    int pace_min_waves = 8;       // tile pacing only pays on long runs
+    int pace_limit_ns = 30000;
+    Tune() {
+        if (const char* v = getenv("B200FP8_PACE_MIN_WAVES")) pace_min_waves = atoi(v);
+        if (const char* v = getenv("B200FP8_PACE_LIMIT_NS")) pace_limit_ns = atoi(v);
+        if (const char* v = getenv("B200FP8_DEBUG")) debug = atoi(v);
+        if (const char* v = getenv("B200FP8_WAIT_HINT_NS")) wait_hint_ns = atoi(v);
+        if (const char* v = getenv("B200FP8_GROUP_M_PAIR")) group_m_pair = atoi(v) > 0 ? atoi(v) : group_m_pair;
+        if (const char* v = getenv("B200FP8_GROUP_M_SINGLE")) group_m_single = atoi(v) > 0 ? atoi(v) : group_m_single;
+    }
+};
+const Tune& tune() { static Tune t; return t; }
+long long* g_trace = nullptr;   // diagnostics buffer (B200FP8_DEBUG & 64)
+
+template <int BN, int STAGES, int CTAS, int NACC>
+cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
                         cudaStream_t stream) {
-    using L = GemmSmem<BN, STAGES, CTAS>;
+    using L = GemmSmem<BN, STAGES, CTAS, NACC>;
     static bool attr_done[kMaxDevices] = {};
-    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS>;
+    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev]) {
@@ -101,8 +126,14 @@ cudaError_t launch_main(const DeviceCtx& ctx, int m, int k, int n, const void* a
     args.M = m; args.N = n; args.K = k;
     args.num_k_blocks = (k + kBlockK - 1) / kBlockK;
     args.m_tiles = (m + kTileM * CTAS - 1) / (kTileM * CTAS);
-    args.n_tiles = (n + BN - 1) / BN;
-    args.group_m = (CTAS == 2) ? 8 : 16;
+    args.n_tiles = (n + L::kTileN - 1) / L::kTileN;
+    args.group_m = (CTAS == 2) ? tune().group_m_pair : tune().group_m_single;
+    args.wait_hint_ns = static_cast<uint32_t>(tune().wait_hint_ns);
+    args.debug = tune().debug;
+    if (args.debug & (64 | 128)) {
+        if (!g_trace) { cudaMalloc(&g_trace, 3 * 4096 * sizeof(long long)); cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long)); }
+        args.trace = g_trace;
+    }
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
     args.tma_store = ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
     args.C = c; args.ldc = ldc; args.status = ctx.status;
@@ -121,6 +152,18 @@ cudaError_t launch_main(const DeviceCtx& ctx, int m, int k, int n, const void* a
     int units = ctx.sm_count / CTAS;                     // CTAs (or pairs) resident at once
     if (max_ctas > 0 && max_ctas / CTAS < units) units = max_ctas / CTAS > 0 ? max_ctas / CTAS : 1;
     if (tiles < units) units = static_cast<int>(tiles);
+
+    // tile pacing for long persistent runs (pairs only): a fresh zeroed counter per launch, stream-ordered
+    if (CTAS == 2 && tune().pace_min_waves > 0 && tiles >= static_cast<long long>(tune().pace_min_waves) * units) {
+        unsigned int* slot;
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            slot = ctx.pace + (ctx.pace_next++ % kPaceSlots);
+        }
+        if ((e = cudaMemsetAsync(slot, 0, sizeof(unsigned int), stream)) != cudaSuccess) return e;
+        args.pace = slot;
+        args.pace_limit_ns = static_cast<unsigned int>(tune().pace_limit_ns);
+    }
 
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(units * CTAS), 1, 1);
@@ -156,7 +199,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     const int split_k = opt ? opt->split_k : 0;
     const int max_ctas = opt ? opt->max_ctas : 0;
     if (depth != 0 && depth != 2 && depth != 4) return cudaErrorInvalidValue;
-    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_SKINNY) return cudaErrorInvalidValue;
+    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_PAIR_N512) return cudaErrorInvalidValue;
     if (split_k < 0 || max_ctas < 0) return cudaErrorInvalidValue;
 
     DeviceCtx* ctx = nullptr;
@@ -166,15 +209,19 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     if (kernel == B200FP8_KERNEL_AUTO) {
         const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
         const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
+        const long long wide_tiles = static_cast<long long>((m + 255) / 256) * ((n + 511) / 512);
         if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
+        // long runs are power-limited: the wide tile moves a quarter less data per flop
+        else if (wide_tiles >= 16LL * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N512;
         else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
         else if (n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
     if (kernel == B200FP8_KERNEL_SKINNY && m > kSkinnyMaxM) return cudaErrorInvalidValue;
 
-#define B200FP8_LAUNCH(BN, ST, CT) \
-    launch_main<BN, ST, CT>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, stream)
+#define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
+#define B200FP8_LAUNCH4(BN, ST, CT, NA) \
+    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, stream)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);
@@ -182,6 +229,8 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
             return depth == 2 ? B200FP8_LAUNCH(128, 2, 1) : depth == 4 ? B200FP8_LAUNCH(128, 4, 1) : B200FP8_LAUNCH(128, 6, 1);
         case B200FP8_KERNEL_PAIR_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 2) : depth == 4 ? B200FP8_LAUNCH(256, 4, 2) : B200FP8_LAUNCH(256, 6, 2);
+        case B200FP8_KERNEL_PAIR_N512:
+            return depth == 2 ? B200FP8_LAUNCH4(256, 2, 2, 2) : B200FP8_LAUNCH4(256, 4, 2, 2);
         case B200FP8_KERNEL_SKINNY: {
             e = launch_skinny(ctx->sm_count, ctx->status, g_encode, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
                               depth, split_k, stream);
@@ -192,6 +241,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
             return cudaErrorInvalidValue;
     }
 #undef B200FP8_LAUNCH
+#undef B200FP8_LAUNCH4
 }
 
 cudaError_t ensure(void** p, size_t* have, size_t want) {
@@ -310,6 +360,9 @@ int b200fp8_device_status(int* status, int reset) {
 }
 
 long long b200fp8_launch_count(void) { return t_launches; }
+
+// diagnostics: device pointer of the k-block timestamp trace (B200FP8_DEBUG & 64), or NULL
+void* b200fp8_debug_trace(void) { return g_trace; }
 
 const char* b200fp8_version(void) { return "b200fp8 0.1 sm_100a"; }
 

@@ -71,7 +71,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     const int stages = args.stages;
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // provably warp-uniform
     const int lane = threadIdx.x & 31;
     const bool clustered = args.splits > 1;
 
@@ -120,8 +120,8 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                 ok = false;
                 break;
             }
-            if (lane == 0) {
-                const uint32_t b_dst = smem_base + s * L::kStageBytes;
+            const uint32_t b_dst = smem_base + s * L::kStageBytes;
+            if (ptx::elect_one()) {
                 ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kStageBytes);
                 ptx::tma_load_2d(b_dst, &tmap_b, kb * kBlockK, n0, bar_full + 8 * s);
                 ptx::tma_load_2d(b_dst + L::kBBytes, &tmap_a, kb * kBlockK, 0, bar_full + 8 * s);
@@ -150,10 +150,10 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                 break;
             }
             ptx::tc_fence_after();
-            if (lane == 0) {
-                const uint32_t b_src = smem_base + s * L::kStageBytes;
-                const uint64_t adesc = ptx::umma_desc_k128(b_src);                 // 128 rows of B
-                const uint64_t bdesc = ptx::umma_desc_k128(b_src + L::kBBytes);    // MP rows of A
+            const uint32_t b_src = smem_base + s * L::kStageBytes;
+            const uint64_t adesc = ptx::umma_desc_k128(b_src);                 // 128 rows of B
+            const uint64_t bdesc = ptx::umma_desc_k128(b_src + L::kBBytes);    // MP rows of A
+            if (ptx::elect_one()) {
 #pragma unroll
                 for (int k = 0; k < kBlockK / 32; ++k)
                     ptx::umma_f8<1>(tmem_base, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb > kb0) || (k > 0));
@@ -162,7 +162,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
             __syncwarp();
             if (++s == stages) { s = 0; ph ^= 1u; }
         }
-        if (ok && lane == 0) ptx::umma_commit(bar_acc);
+        if (ok && ptx::elect_one()) ptx::umma_commit(bar_acc);
         __syncwarp();
     } else {
         // ---------------- epilogue: 128 threads, thread = one column n of C ----------------

@@ -15,6 +15,12 @@
 // CTAS == 2 pairs two CTAs of a cluster on a 256 x BN tile (cta_group::2): each CTA loads
 // its own 128 rows of A and its own half of the B tile (no multicast), the leader CTA
 // issues the MMAs for both, and each CTA drains its own 128 accumulator rows.
+// NACC == 2 widens the tile to 256 x (2*BN): both TMEM accumulator slots belong to the same
+// tile (columns [0,BN) and [BN,2BN)), every A k-block feeds two MMAs, and shared-memory,
+// L2 and HBM traffic per flop drop by a quarter; the price is that the epilogue of a tile
+// overlaps only the head of the next tile's main loop instead of all of it.  The wide tile
+// wins on large problems, where the GPU runs at its power limit and energy per flop
+// decides the clock.
 //
 // Every wait on an mbarrier is bounded: after about two seconds the waiting warp records a
 // code in the device status word, raises a CTA-wide abort flag and leaves its loop, so a
@@ -35,9 +41,15 @@ struct GemmArgs {
     int group_m;          // rasterisation: tiles are walked down `group_m` M-tiles before moving along N
     uint32_t idesc;       // UMMA instruction descriptor (dtype pair, tile shape)
     int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
+    uint32_t wait_hint_ns; // suspend-time hint for long mbarrier waits (0 = plain polling)
+    int debug;            // diagnostics only (results become wrong): 1 skip TMA loads, 2 skip C stores, 4 skip MMAs,
+                          // 64 record per-k-block clock64 stamps of CTA 0's MMA warp in `trace`
     float* C;
     long long ldc;
     int* status;          // device status word: 0 = ok, else first error code recorded
+    unsigned int* pace;   // tile-pacing counter (zero at launch) or nullptr: see the producer warp
+    unsigned int pace_limit_ns;
+    long long* trace;     // diagnostics (debug & 64): per k-block clock64 stamps of CTA 0's MMA thread
 };
 
 enum : int {
@@ -54,14 +66,28 @@ constexpr int kEpiWarps = 4;
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
+// Bounded wait on an mbarrier phase.  A few immediate tests first (the common case: the phase
+// is already complete or completes within the round trip), then tests that let the hardware
+// suspend the thread for up to `hint_ns` at a time, which keeps waiting warps from burning
+// issue slots and power.  Gives up after kWaitLimitNs or when the CTA's abort flag is raised.
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                             bool cluster_scope) {
-    uint32_t spins = 0;
-    uint64_t t0 = 0;
-    for (;;) {
+                                             bool cluster_scope, uint32_t hint_ns = 0) {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
         const bool ok = cluster_scope ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity);
         if (ok) return true;
-        if ((++spins & 0x3FFu) == 0) {
+    }
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    const uint32_t check_mask = hint_ns ? 0x7u : 0x3FFu;
+    for (;;) {
+        bool ok;
+        if (hint_ns)
+            ok = cluster_scope ? ptx::mbar_try_wait_cluster_hint(bar, parity, hint_ns) : ptx::mbar_try_wait_hint(bar, parity, hint_ns);
+        else
+            ok = cluster_scope ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity);
+        if (ok) return true;
+        if ((++spins & check_mask) == 0) {
             if (*abort_flag) return false;
             const uint64_t now = ptx::globaltimer_ns();
             if (t0 == 0) t0 = now;
@@ -76,12 +102,12 @@ __device__ __forceinline__ void record_failure(int* status, volatile int* abort_
     __threadfence_block();
 }
 
-template <int BN, int STAGES, int CTAS>
+template <int BN, int STAGES, int CTAS, int NACC>
 struct GemmSmem {
     static constexpr int kABytes = kTileM * kBlockK;
-    static constexpr int kBRows = BN / CTAS;
+    static constexpr int kBRows = BN / CTAS;                 // rows of one B sub-tile held by this CTA
     static constexpr int kBBytes = kBRows * kBlockK;
-    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStageBytes = kABytes + NACC * kBBytes;
     static constexpr int kTxBytes = kStageBytes * CTAS;      // bytes landing per ring slot across the pair
     static constexpr int kEpiBufBytes = 32 * 32 * 4;         // one 32x32 FP32 box
     static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
@@ -93,23 +119,24 @@ struct GemmSmem {
     static constexpr int kAbortOff = kTmemSlotOff + 8;
     static constexpr int kTotal = kAbortOff + 8;
     static constexpr int kDynamicBytes = kTotal + 1024;      // slack for manual 1024-byte alignment
-    static constexpr int kTmemCols = 2 * BN;                 // two accumulator buffers (256 or 512: powers of 2)
+    static constexpr int kTmemCols = 2 * BN;                 // two accumulator slots (256 or 512 columns: powers of 2)
+    static constexpr int kTileN = BN * NACC;                 // columns of C per tile
 };
 
-template <int BN, int STAGES, int CTAS>
+template <int BN, int STAGES, int CTAS, int NACC>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c,
                        const GemmArgs args)
 {
-    using L = GemmSmem<BN, STAGES, CTAS>;
-    static_assert(BN % 32 == 0 && BN <= 256 && (BN / CTAS) % 8 == 0, "tile");
+    using L = GemmSmem<BN, STAGES, CTAS, NACC>;
+    static_assert(BN % 32 == 0 && BN <= 256 && (BN / CTAS) % 8 == 0 && (NACC == 1 || NACC == 2), "tile");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // provably warp-uniform
     const int lane = threadIdx.x & 31;
     const uint32_t rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
     const bool pair = (CTAS == 2);
@@ -162,43 +189,74 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int m_blk = first_m + r % gsz;
         const int n_blk = r / gsz;
         m0 = m_blk * (kTileM * CTAS) + static_cast<int>(rank) * kTileM;
-        n0 = n_blk * BN;
+        n0 = n_blk * L::kTileN;
     };
+    // Accumulator slot bookkeeping.  NACC == 1: tile `it` owns slot it & 1 (its (it >> 1)-th use).
+    // NACC == 2: every tile owns both slots (slot j holds columns [j*BN, (j+1)*BN); use number = it).
+    auto slot_of = [&](int it, int j) { return NACC == 1 ? (it & 1) : j; };
+    auto use_parity = [&](int it) { return static_cast<uint32_t>((NACC == 1 ? (it >> 1) : it) & 1); };
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer: warp-uniform loop, one elected lane issues ----------------
         const uint32_t full0 = pair ? ptx::mapa(bar_full, 0) : bar_full;   // the leader's full barriers
         int s = 0;
         uint32_t ph = 0;
         int issued = 0;
         bool ok = true;
-        for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+        int it = 0;
+        for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
             int m0, n0;
             tile_coords(t, m0, n0);
             const int nb0 = n0 + static_cast<int>(rank) * L::kBRows;
+            if (args.pace != nullptr && rank == 0 && it > 0) {
+                // Tile pacing: CTAs that share operand panels through L2 only profit while they sweep K
+                // together, and small systematic speed differences between SMs pull them apart over a
+                // long run.  Before a new tile every leader announces itself and waits -- briefly and
+                // never longer than pace_limit_ns -- for the others.  Purely a performance hint: running
+                // out of patience just means starting the tile unaligned.
+                const unsigned int target = static_cast<unsigned int>(it) * static_cast<unsigned int>(tile_step);
+                if (ptx::elect_one()) atomicAdd(args.pace, 1u);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (*reinterpret_cast<volatile unsigned int*>(args.pace) < target &&
+                       ptx::globaltimer_ns() - t0 < args.pace_limit_ns)
+                    __nanosleep(256);
+                __syncwarp();
+            }
             for (int kb = 0; kb < nkb; ++kb) {
-                if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, pair)) {
+                if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusProducerTimeout);
                     ok = false;
                     break;
                 }
-                if (lane == 0) {
-                    const uint32_t a_dst = smem_base + L::kRingOff + s * L::kStageBytes;
-                    const uint32_t b_dst = a_dst + L::kABytes;
-                    if (pair) {
+                const uint32_t a_dst = smem_base + L::kRingOff + s * L::kStageBytes;
+                const uint32_t b_dst = a_dst + L::kABytes;
+                if (ptx::elect_one()) {
+                    if (args.debug & 1) {
+                        if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
+                    } else if (pair) {
                         if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kTxBytes);
                         ptx::tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, m0, full0 + 8 * s);
-                        ptx::tma_load_2d_pair(b_dst, &tmap_b, kb * kBlockK, nb0, full0 + 8 * s);
+#pragma unroll
+                        for (int j = 0; j < NACC; ++j)
+                            ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, &tmap_b, kb * kBlockK, nb0 + j * BN, full0 + 8 * s);
                     } else {
                         ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kTxBytes);
                         ptx::tma_load_2d(a_dst, &tmap_a, kb * kBlockK, m0, bar_full + 8 * s);
-                        ptx::tma_load_2d(b_dst, &tmap_b, kb * kBlockK, nb0, bar_full + 8 * s);
+#pragma unroll
+                        for (int j = 0; j < NACC; ++j)
+                            ptx::tma_load_2d(b_dst + j * L::kBBytes, &tmap_b, kb * kBlockK, nb0 + j * BN, bar_full + 8 * s);
                     }
                 }
                 __syncwarp();
                 ++issued;
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
             }
+        }
+        if (args.pace != nullptr && rank == 0) {
+            // announce the iterations this pair does not have, so that nobody waits for it
+            const int max_it = (num_tiles + tile_step - 1) / tile_step;
+            if (it < max_it && ptx::elect_one()) atomicAdd(args.pace, static_cast<unsigned int>(max_it - it));
+            __syncwarp();
         }
         if (!ok && rank == 0) {
             // leave no copy in flight into this CTA's shared memory: wait (bounded) for the slots armed last
@@ -211,44 +269,69 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer (leader CTA only) ----------------
+        // ---------------- MMA issuer: leader CTA, warp-uniform loop, one elected lane issues ----------------
         if (rank == 0) {
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
             bool ok = true;
             for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
-                const int buf = it & 1;
-                const uint32_t aph = (it >> 1) & 1;
-                if (!wait_bounded(bar_tempty + 8 * buf, aph ^ 1u, abort_flag, pair)) {
+                // slot 0 of this tile must have been drained; slot 1 (NACC == 2) is awaited just before its first MMA
+                if (!wait_bounded(bar_tempty + 8 * slot_of(it, 0), use_parity(it) ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusMmaTimeout);
                     break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                if ((args.debug & 128) && lane == 0 && it < 128) args.trace[(blockIdx.x / CTAS) * 128 + it] = static_cast<long long>(ptx::globaltimer_ns());
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!wait_bounded(bar_full + 8 * s, ph, abort_flag, pair)) {
+                    long long tr0 = 0, tr1 = 0;
+                    if ((args.debug & 64) && blockIdx.x == 0) tr0 = clock64();
+                    if (!wait_bounded(bar_full + 8 * s, ph, abort_flag, pair, args.wait_hint_ns)) {
                         record_failure(args.status, abort_flag, kStatusMmaTimeout);
                         ok = false;
                         break;
                     }
+                    if ((args.debug & 64) && blockIdx.x == 0) tr1 = clock64();
                     ptx::tc_fence_after();
-                    if (lane == 0) {
-                        const uint32_t a_src = smem_base + L::kRingOff + s * L::kStageBytes;
-                        const uint64_t adesc = ptx::umma_desc_k128(a_src);
-                        const uint64_t bdesc = ptx::umma_desc_k128(a_src + L::kABytes);
+                    const uint32_t a_src = smem_base + L::kRingOff + s * L::kStageBytes;
+                    const uint64_t adesc = ptx::umma_desc_k128(a_src);
 #pragma unroll
-                        for (int k = 0; k < kBlockK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
-                            ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                    for (int j = 0; j < NACC; ++j) {
+                        if (NACC == 2 && j == 1 && kb == 0) {
+                            if (!wait_bounded(bar_tempty + 8, use_parity(it) ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
+                                record_failure(args.status, abort_flag, kStatusMmaTimeout);
+                                ok = false;
+                                break;
+                            }
+                            ptx::tc_fence_after();
+                        }
+                        const uint32_t d_tmem = tmem_base + slot_of(it, j) * BN;
+                        const uint64_t bdesc = ptx::umma_desc_k128(a_src + L::kABytes + j * L::kBBytes);
+                        if (ptx::elect_one()) {
+#pragma unroll
+                            for (int k = 0; k < kBlockK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
+                                if (!(args.debug & 4)) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                        }
+                        __syncwarp();
+                    }
+                    if (!ok) break;
+                    if (ptx::elect_one()) {
                         if (pair) ptx::umma_commit_pair(bar_empty + 8 * s, 0x3);
                         else ptx::umma_commit(bar_empty + 8 * s);
                     }
                     __syncwarp();
+                    if ((args.debug & 64) && blockIdx.x == 0 && lane == 0) {
+                        const int idx = it * nkb + kb;
+                        if (idx < 4096) { args.trace[3 * idx] = tr0; args.trace[3 * idx + 1] = tr1; args.trace[3 * idx + 2] = clock64(); }
+                    }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
-                if (ok && lane == 0) {
-                    if (pair) ptx::umma_commit_pair(bar_tfull + 8 * buf, 0x3);
-                    else ptx::umma_commit(bar_tfull + 8 * buf);
+                if (ok && ptx::elect_one()) {
+#pragma unroll
+                    for (int j = 0; j < NACC; ++j) {
+                        if (pair) ptx::umma_commit_pair(bar_tfull + 8 * slot_of(it, j), 0x3);
+                        else ptx::umma_commit(bar_tfull + 8 * slot_of(it, j));
+                    }
                 }
                 __syncwarp();
             }
@@ -258,60 +341,66 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int q = warp & 3;                                   // TMEM lane quarter this warp may read
         const uint32_t stage_base = smem_base + L::kEpiOff + q * (2 * L::kEpiBufBytes);
         const uint32_t tempty0 = pair ? ptx::mapa(bar_tempty, 0) : bar_tempty;
+        const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
         int it = 0;
-        for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+        bool ok = true;
+        for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
             int m0, n0;
             tile_coords(t, m0, n0);
-            const int buf = it & 1;
-            const uint32_t aph = (it >> 1) & 1;
-            if (!wait_bounded(bar_tfull + 8 * buf, aph, abort_flag, pair)) {
-                record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
-                break;
-            }
-            ptx::tc_fence_after();
             const int row0 = m0 + q * 32;
-            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(t_addr + c * 32, v);
-                ptx::tmem_ld_wait();
-                if (c == BN / 32 - 1) {
-                    // accumulator fully read: hand the TMEM buffer back to the MMA warp
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (pair) ptx::mbar_arrive_cluster(tempty0 + 8 * buf);
-                        else ptx::mbar_arrive(bar_tempty + 8 * buf);
-                    }
+            for (int j = 0; j < NACC; ++j) {
+                const int slot = slot_of(it, j);
+                if (!wait_bounded(bar_tfull + 8 * slot, use_parity(it), abort_flag, pair, args.wait_hint_ns)) {
+                    record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
+                    ok = false;
+                    break;
                 }
-                const int col0 = n0 + c * 32;
-                if (args.tma_store) {
-                    const uint32_t sb = stage_base + (c & 1) * L::kEpiBufBytes;
-                    if (lane == 0) ptx::bulk_wait_group_read<1>();     // the store that last used this buffer has read it
-                    __syncwarp();
-                    const uint32_t row_addr = sb + lane * 128;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        ptx::st_shared_v4(row_addr + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (row0 < args.M && col0 < args.N) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
-                        ptx::bulk_commit_group();
+                __syncwarp();
+                ptx::tc_fence_after();
+                const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(t_addr + c * 32, v);
+                    ptx::tmem_ld_wait();
+                    if (c == BN / 32 - 1) {
+                        // slot fully read: hand it back to the MMA warp
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (pair) ptx::mbar_arrive_cluster(tempty0 + 8 * slot);
+                            else ptx::mbar_arrive(bar_tempty + 8 * slot);
+                        }
                     }
-                } else {
-                    const int row = row0 + lane;
-                    if (row < args.M) {
-                        float* dst = args.C + static_cast<long long>(row) * args.ldc + col0;
+                    const int col0 = n0 + j * BN + c * 32;
+                    if (args.tma_store) {
+                        const uint32_t sb = stage_base + (c & 1) * L::kEpiBufBytes;
+                        if (issuer) ptx::bulk_wait_group_read<1>();    // the store that last used this buffer has read it
+                        __syncwarp();
+                        const uint32_t row_addr = sb + lane * 128;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < args.N) dst[j] = __uint_as_float(v[j]);
+                        for (int i = 0; i < 8; ++i)
+                            ptx::st_shared_v4(row_addr + ((i ^ (lane & 7)) << 4), v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (issuer) {
+                            if (row0 < args.M && col0 < args.N && !(args.debug & 2)) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                            ptx::bulk_commit_group();
+                        }
+                    } else {
+                        const int row = row0 + lane;
+                        if (row < args.M) {
+                            float* dst = args.C + static_cast<long long>(row) * args.ldc + col0;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < args.N) dst[i] = __uint_as_float(v[i]);
+                        }
                     }
                 }
             }
         }
-        if (lane == 0) ptx::bulk_wait_group<0>();                 // all stores of this warp are complete
+        if (issuer) ptx::bulk_wait_group<0>();                    // all stores of this warp are complete
         __syncwarp();
     }
 
@@ -320,6 +409,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncthreads();
     if (pair) { ptx::cluster_arrive(); ptx::cluster_wait(); }
     if (warp == 1) {
+        __syncwarp();
         ptx::tc_fence_after();
         ptx::tmem_dealloc<CTAS>(tmem_base, L::kTmemCols);
     }

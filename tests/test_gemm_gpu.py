@@ -88,7 +88,7 @@ def test_golden_fixture_through_reference_api(g, oracle, path, entry):
 
 # ---------------------------------------------------------------- exact known answers
 
-@pytest.mark.parametrize("kernel", [1, 2, 3, 4])
+@pytest.mark.parametrize("kernel", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("fa,fb", COMBOS)
 def test_one_hot_rows_select_columns_exactly(g, oracle, kernel, fa, fb):
     m, k, n = (64, 256, 384) if kernel == 4 else (384, 256, 640)
@@ -103,7 +103,7 @@ def test_one_hot_rows_select_columns_exactly(g, oracle, kernel, fa, fb):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("kernel", [2, 3, 4])
+@pytest.mark.parametrize("kernel", [2, 3, 4, 5])
 def test_powers_of_two_sum_exactly(g, oracle, kernel):
     m, k, n = (128, 512, 256) if kernel == 4 else (256, 512, 512)
     rng = np.random.default_rng(5)
@@ -133,6 +133,7 @@ def test_special_values_propagate(g, oracle):
     (2, 2, (256, 384, 256)), (2, 4, (384, 1040, 200)), (2, 0, (130, 48, 131)),
     (1, 2, (300, 528, 516)), (1, 4, (256, 2064, 512)), (1, 0, (129, 144, 260)),
     (3, 2, (512, 400, 512)), (3, 4, (300, 208, 516)), (3, 0, (1030, 1024, 770)),
+    (5, 2, (512, 400, 1024)), (5, 4, (300, 208, 1030)), (5, 0, (1030, 1024, 1540)),
     (4, 0, (16, 1024, 1000)), (4, 2, (100, 2048, 384)), (4, 4, (128, 528, 260)),
     (0, 0, (640, 256, 896)),
 ])
@@ -152,7 +153,7 @@ def test_ragged_m(g, oracle, m):
 
 
 @pytest.mark.parametrize("k", [16, 32, 48, 64, 112, 128, 144, 256, 4096 + 16])
-@pytest.mark.parametrize("kernel", [2, 3, 4])
+@pytest.mark.parametrize("kernel", [2, 3, 4, 5])
 def test_k_sweep_including_tails(g, oracle, k, kernel):
     m, n = (48, 200) if kernel == 4 else (260, 520)
     a, b = random_operands(g, m, k, n, 0, 1, seed=k)
@@ -185,6 +186,7 @@ def test_zero_k_and_empty(g):
 # ---------------------------------------------------------------- memory safety: canaries instead of a sanitizer
 
 @pytest.mark.parametrize("kernel,m,n,ldc", [(2, 130, 132, 160), (3, 300, 260, 264), (1, 129, 257, 257), (4, 20, 130, 131),
+                                            (5, 300, 772, 776), (5, 257, 515, 515),
                                             (4, 100, 260, 272)])
 def test_no_write_outside_c(g, oracle, kernel, m, n, ldc):
     k = 192
@@ -303,14 +305,15 @@ def test_config5_n_shards_equal_unsharded_bitwise(g, oracle):
     pkg = load_package()
     m, k, n = 2048, 4096, 4096
     a, b = random_operands(g, m, k, n, 0, 0, seed=0xB200F800 + 80)
-    full = run(g, a, b, m, k, n, kernel=3)
-    for world in (2, 4, 8):
-        out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
-        for r in range(world):
-            sh = pkg.shard.column_shard(n, r, world)
-            g.gemm_ex(a, b[sh.n_begin:sh.n_end], out[:, sh.n_begin:sh.n_end], kernel=3, ldc=n)
-        torch.cuda.synchronize()
-        assert torch.equal(out, full)
+    for kernel in (3, 5):
+        full = run(g, a, b, m, k, n, kernel=kernel)
+        for world in (2, 4, 8):
+            out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+            for r in range(world):
+                sh = pkg.shard.column_shard(n, r, world)
+                g.gemm_ex(a, b[sh.n_begin:sh.n_end], out[:, sh.n_begin:sh.n_end], kernel=kernel, ldc=n)
+            torch.cuda.synchronize()
+            assert torch.equal(out, full)
     sampled_check(oracle, a, b, full, 0, 0, rows=2, cols=2, points=1024)
 
 
