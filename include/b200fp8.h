@@ -108,6 +108,36 @@ int b200fp8_fill_normal(void* dst, long long count, int dtype, float sigma, unsi
  */
 int b200fp8_device_status(int* status, int reset);
 
+/*
+ * The same GEMM (lda = ldb = k, ldc = n) for callers that are not allowed to
+ * allocate device memory.  This entry point has no counterpart in the
+ * reference.  Who needs it: a plugin loaded into a host program that reserved
+ * the whole device for its own memory pool and forbids cudaMalloc behind its
+ * back, a service with a hard per-process memory budget, or a latency-critical
+ * loop that cannot take the device-wide synchronisation an allocation or a
+ * free may imply.  The other entry points allocate a few small per-device
+ * buffers on first use; this one calls no cudaMalloc, cudaFree or allocating
+ * library routine, ever.
+ *
+ * Its scratch memory -- the counter the CTA-pair kernels use to keep their
+ * tiles in step -- lives in a static 256-byte device array inside the
+ * library (every GPU that loads the library holds those 256 bytes until the
+ * process exits).  Consequences:
+ *   - all calls on one device share that array: two calls whose kernels
+ *     overlap on the GPU (different streams) race on it; issue them on one
+ *     stream, or otherwise keep them from overlapping;
+ *   - the first call on each device resolves the array's device address and
+ *     prepares the kernels; make that first call outside any stream capture;
+ *   - at most 2^24 output tiles (256 x 256 elements each) per call; larger
+ *     problems are rejected with cudaErrorInvalidValue and a message on stderr.
+ * Always runs a CTA-pair kernel, whatever the shape.  `status_word` is an
+ * optional DEVICE int the caller owns and has zeroed: a kernel whose bounded
+ * wait runs out stores its code there (the role b200fp8_device_status plays
+ * for the other entry points); pass NULL to do without.
+ */
+int b200fp8_gemm_rowcol_f32_noalloc(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype,
+                                    float* c, int* status_word, void* stream);
+
 /* Number of this library's kernels launched by the calling thread so far. */
 long long b200fp8_launch_count(void);
 

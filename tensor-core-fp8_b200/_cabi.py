@@ -28,6 +28,7 @@ DECLARED_SYMBOLS = (
     "b200fp8_gemm_rowcol_f32",
     "b200fp8_gemm_rowcol_f32_ex",
     "b200fp8_gemm_rowcol_f32_host",
+    "b200fp8_gemm_rowcol_f32_noalloc",
     "b200fp8_fill_normal",
     "b200fp8_device_status",
     "b200fp8_launch_count",
@@ -71,6 +72,7 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_gemm_rowcol_f32_ex.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ll,
                                                  ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
+        L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
         L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]
         L.b200fp8_device_status.argtypes = [ctypes.POINTER(ci), ci]
         L.b200fp8_launch_count.restype = ll

@@ -335,6 +335,138 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     return first;
 }
 
+// ---------------------------------------------------------------------------------------------
+// b200fp8_gemm_rowcol_f32_noalloc: the pair kernels with their scratch memory in a static device
+// array, for callers that must not allocate (see include/b200fp8.h).  Nothing on this path calls
+// cudaMalloc / cudaFree or touches the library's per-device context, which owns allocated buffers.
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace b200fp8 {
+namespace {
+
+constexpr int kNoAllocScratchWords = 64;                    // 256 bytes per GPU that loads the library
+constexpr long long kNoAllocMaxTiles = 1LL << 24;           // tiles per call the pacing counter is specified for
+
+// Word 0 is the tile-pacing counter of the pair kernels (must be zero when a launch starts).
+// The remaining words are reserved.  Every call on a device shares this one array.
+static __device__ __align__(256) unsigned int g_noalloc_scratch[kNoAllocScratchWords];
+
+struct NoAllocDevice {
+    bool ready = false;
+    int sm_count = 0;
+    unsigned int* scratch = nullptr;    // DEVICE address of g_noalloc_scratch on this device
+};
+NoAllocDevice g_noalloc[kMaxDevices];
+
+template <int BN, int STAGES, int NACC>
+cudaError_t noalloc_prepare_kernel() {
+    return cudaFuncSetAttribute(gemm_fp8_rowcol_kernel<BN, STAGES, 2, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                GemmSmem<BN, STAGES, 2, NACC>::kDynamicBytes);
+}
+
+// One-time set-up per device, with that device current: resolves the device address of the static
+// array (the array's name is only a host-side handle and must never be given to a kernel),
+// raises the kernels' shared-memory limit and zeroes the array.
+cudaError_t noalloc_device(NoAllocDevice** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    NoAllocDevice& d = g_noalloc[dev];
+    if (!d.ready) {
+        int major = 0;
+        if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) return e;
+        if (major != 10) return cudaErrorNoKernelImageForDevice;
+        if ((e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+        if ((e = load_encode()) != cudaSuccess) return e;
+        void* ptr = nullptr;
+        if ((e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch)) != cudaSuccess) return e;
+        if ((e = noalloc_prepare_kernel<256, 6, 1>()) != cudaSuccess) return e;
+        if ((e = noalloc_prepare_kernel<256, 4, 2>()) != cudaSuccess) return e;
+        if ((e = cudaMemset(ptr, 0, sizeof(unsigned int) * kNoAllocScratchWords)) != cudaSuccess) return e;
+        d.scratch = static_cast<unsigned int*>(ptr);
+        d.ready = true;
+    }
+    *out = &d;
+    return cudaSuccess;
+}
+
+template <int BN, int STAGES, int NACC>
+cudaError_t noalloc_launch(const NoAllocDevice& d, int m, int k, int n, const void* a, const void* b, float* c,
+                           int a_dtype, int b_dtype, int* status_word, cudaStream_t stream) {
+    using L = GemmSmem<BN, STAGES, 2, NACC>;
+    GemmArgs args{};
+    args.M = m; args.N = n; args.K = k;
+    args.num_k_blocks = (k + kBlockK - 1) / kBlockK;
+    args.m_tiles = (m + 2 * kTileM - 1) / (2 * kTileM);
+    args.n_tiles = (n + L::kTileN - 1) / L::kTileN;
+    args.group_m = 16;
+    args.idesc = make_idesc_f8(a_dtype, b_dtype, 2 * kTileM, BN);
+    args.tma_store = ((n % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
+    args.C = c; args.ldc = n; args.status = status_word;
+    const long long tiles = static_cast<long long>(args.m_tiles) * args.n_tiles;
+    if (tiles > kNoAllocMaxTiles) {
+        fprintf(stderr, "b200fp8_gemm_rowcol_f32_noalloc: %lld output tiles exceed the maximum of %lld this entry point supports\n",
+                tiles, kNoAllocMaxTiles);
+        return cudaErrorInvalidValue;
+    }
+    CUtensorMap ta, tb, tc;
+    cudaError_t e;
+    if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, k, kBlockK, kTileM)) != cudaSuccess) return e;
+    if ((e = encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, k, kBlockK, L::kBRows)) != cudaSuccess) return e;
+    if (args.tma_store) {
+        if ((e = encode_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, c, n, m, n, 32, 32)) != cudaSuccess) return e;
+    } else {
+        tc = ta;
+    }
+    int units = d.sm_count / 2;
+    if (tiles < units) units = static_cast<int>(tiles);
+    if (tiles >= 8LL * units) {
+        // the counter keeps whatever the previous call left: it has to start from zero
+        if ((e = cudaMemsetAsync(d.scratch, 0, sizeof(unsigned int), stream)) != cudaSuccess) return e;
+        args.pace = d.scratch;
+        args.pace_limit_ns = 30000;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(units * 2), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kDynamicBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, gemm_fp8_rowcol_kernel<BN, STAGES, 2, NACC>, ta, tb, tc, args);
+    if (e == cudaSuccess) ++t_launches;
+    return e;
+}
+
+}  // namespace
+}  // namespace b200fp8
+
+extern "C" {
+
+int b200fp8_gemm_rowcol_f32_noalloc(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype,
+                                    float* c, int* status_word, void* stream) {
+    if (m < 0 || n < 0 || k < 0 || !valid_dtype(a_dtype) || !valid_dtype(b_dtype)) return cudaErrorInvalidValue;
+    if (m == 0 || n == 0) return cudaSuccess;
+    if (!c || !a || !b || k == 0 || (k % 16)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(b) % 16) ||
+        (reinterpret_cast<uintptr_t>(c) % 4) || (reinterpret_cast<uintptr_t>(status_word) % 4))
+        return cudaErrorInvalidValue;
+    NoAllocDevice* d = nullptr;
+    cudaError_t e = noalloc_device(&d);
+    if (e != cudaSuccess) return e;
+    const long long wide_tiles = static_cast<long long>((m + 255) / 256) * ((n + 511) / 512);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (wide_tiles >= 16LL * (d->sm_count / 2) && k >= 8192)
+        return noalloc_launch<256, 4, 2>(*d, m, k, n, a, b, c, a_dtype, b_dtype, status_word, s);
+    return noalloc_launch<256, 6, 1>(*d, m, k, n, a, b, c, a_dtype, b_dtype, status_word, s);
+}
+
 int b200fp8_fill_normal(void* dst, long long count, int dtype, float sigma, unsigned long long seed,
                         unsigned long long index_offset, void* stream) {
     if (count < 0 || !valid_dtype(dtype) || (count > 0 && !dst)) return cudaErrorInvalidValue;
