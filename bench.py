@@ -45,7 +45,11 @@ SEED_BASE = 0xB200F800
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "shard32768": 30.11e9,   # profiles/gemm_fp8_rowcol_kernel__shard32768__launch_list_and_dram.md
+    "gemm8192": 537.6e6,     # profiles/gemm_fp8_rowcol_kernel__gemm8192__full_set.md
+    "skinny16": 67.8e6,      # profiles/gemm_fp8_skinny_kernel__skinny16__full_set.md
+}
 
 
 def measured_peaks():
@@ -128,7 +132,7 @@ def cpu_reference_rate(M, K, N, rows_per_thread: int, seed_a: int, seed_b: int):
     from oracle import fp8_oracle as fo
     threads = fo.max_threads()
     rows = min(M, rows_per_thread * threads)
-    cols = min(N, 256)
+    cols = min(N, 512)
     A = fo.fill_normal(rows * K, fo.E4M3, 1.0, seed_a).reshape(rows, K)
     B = fo.fill_normal(cols * K, fo.E4M3, 1.0, seed_b).reshape(cols, K)
     t0 = time.perf_counter()
@@ -147,7 +151,7 @@ def run_reference(args):
     # bounded sample per step: about a second of work per step on all host threads
     rates = []
     for i in range(args.warmup + args.steps):
-        r, threads, sample, dt = cpu_reference_rate(M, K, N, 8, SEED_BASE + 64, SEED_BASE + 65)
+        r, threads, sample, dt = cpu_reference_rate(M, K, N, 128, SEED_BASE + 64, SEED_BASE + 65)
         if i >= args.warmup:
             rates.append((r, dt))
     total_t = sum(d for _, d in rates)
@@ -339,60 +343,65 @@ def main() -> int:
                              "layout": "[rank][M][N/R] blocks"}
         del full
 
-    # ---- side measurements on rank 0 at N = 1: the 8192^3 target shape and cuBLASLt on the same buffers ----
+    # ---- side measurements on rank 0 at N = 1: the 8192^3 target shape and the bench workload, ours against
+    #      cuBLASLt on the same buffers, ALTERNATING so that both see the same clocks and temperature ----
     if rank == 0 and world == 1 and not args.no_extras:
         extras = {}
         cmp_path = pkg._cabi.CMP_LIB_PATH
         cmp = ctypes.CDLL(cmp_path) if os.path.exists(cmp_path) else None
+        ci, vp, fp = ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)
         if cmp is not None:
-            cmp.b200fp8_cmp_cublaslt.argtypes = [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
-                                                                      ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
-                                                                      ctypes.c_int, ctypes.c_int,
-                                                                      ctypes.POINTER(ctypes.c_float),
-                                                                      ctypes.POINTER(ctypes.c_int), ctypes.c_void_p]
+            cmp.b200fp8_cmp_cublaslt.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci, fp, ctypes.POINTER(ci), vp]
+            cmp.b200fp8_cmp_cublaslt_run.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, fp, vp]
+        stream = torch.cuda.current_stream().cuda_stream
         for name in ("gemm8192", args.workload):
             if name in extras:
                 continue
             m2, k2, n2, _ = WORKLOADS[name]
             if name == args.workload:
                 a2, b2, c2 = a, bs[0], cs[0]
+                n2 = n_local
             else:
                 a2 = torch.empty((m2, k2), dtype=f8, device=dev)
                 b2 = torch.empty((n2, k2), dtype=f8, device=dev)
                 c2 = torch.empty((m2, n2), dtype=torch.float32, device=dev)
                 g.fill_normal(a2, 1.0, seed_a + 7)
                 g.fill_normal(b2, 1.0, seed_b + 7)
-            iters = 10 if 2.0 * m2 * k2 * n2 < 5e12 else 3
-            for _ in range(3):
-                g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(iters):
-                g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
-            e1.record()
-            torch.cuda.synchronize()
-            ours_ms = e0.elapsed_time(e1) / iters
-            entry = {"ms": ours_ms, "tflops": 2.0 * m2 * k2 * n2 / ours_ms / 1e9}
+            fl = 2.0 * m2 * k2 * n2
+            iters = 20 if fl < 5e12 else 3
+            have_cmp = False
             if cmp is not None:
-                best = None
-                for fast in (0, 1):
+                ms = ctypes.c_float(-1)
+                found = ci(0)
+                have_cmp = cmp.b200fp8_cmp_cublaslt(m2, k2, n2, a2.data_ptr(), 0, b2.data_ptr(), 0, c2.data_ptr(), 3, 8, 0,
+                                                    ctypes.byref(ms), ctypes.byref(found), stream) == 0
+            ours, theirs = [], []
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for rnd in range(4):
+                e0.record()
+                for _ in range(iters):
+                    g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+                e1.record()
+                torch.cuda.synchronize()
+                if rnd:                                   # round 0 warms both up
+                    ours.append(e0.elapsed_time(e1) / iters)
+                if have_cmp:
                     ms = ctypes.c_float(-1)
-                    found = ctypes.c_int(0)
-                    rc = cmp.b200fp8_cmp_cublaslt(m2, k2, n2, a2.data_ptr(), 0, b2.data_ptr(), 0, c2.data_ptr(), iters, 8,
-                                                  fast, ctypes.byref(ms), ctypes.byref(found),
-                                                  torch.cuda.current_stream().cuda_stream)
-                    if rc == 0 and (best is None or ms.value < best):
-                        best = ms.value
-                if best:
-                    entry["cublaslt_ms"] = best
-                    entry["cublaslt_tflops"] = 2.0 * m2 * k2 * n2 / best / 1e9
-                    entry["vs_cublaslt"] = best / ours_ms
+                    cmp.b200fp8_cmp_cublaslt_run(m2, k2, n2, a2.data_ptr(), 0, b2.data_ptr(), 0, c2.data_ptr(), iters,
+                                                 ctypes.byref(ms), stream)
+                    if rnd:
+                        theirs.append(ms.value)
+            o = sum(ours) / len(ours)
+            entry = {"ms": o, "tflops": fl / o / 1e9, "protocol": f"3 alternating rounds of {iters} launches each"}
+            if theirs:
+                t_ = sum(theirs) / len(theirs)
+                entry.update({"cublaslt_ms": t_, "cublaslt_tflops": fl / t_ / 1e9, "vs_cublaslt": t_ / o})
             extras[name] = entry
         line["side"] = extras
 
     # ---- the reference's CPU loop timed on this box's host cores (rank 0, N = 1 only) ----
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        r, threads, sample, dt = cpu_reference_rate(M, K, N, 64, seed_a, seed_b)
+        r, threads, sample, dt = cpu_reference_rate(M, K, N, 1024, seed_a, seed_b)
         line["cpu_baseline"] = {"value": r, "unit": "TFLOPS", "cores": threads, "kind": "port",
                                 "sample": sample + f", {dt:.1f} s; the reference's float loop "
                                 "(GEMM/gemm_main.cpp:45-52) restated in oracle/fp8_oracle.c, OpenMP over rows"}

@@ -16,6 +16,19 @@
 
 namespace {
 cudaDataType_t fp8_type(int d) { return d == 0 ? CUDA_R_8F_E4M3 : CUDA_R_8F_E5M2; }
+
+// the candidate chosen by the last b200fp8_cmp_cublaslt call, kept for b200fp8_cmp_cublaslt_run
+struct Chosen {
+    bool valid = false;
+    int m = 0, k = 0, n = 0, a_dtype = 0, b_dtype = 0;
+    cublasLtMatmulDesc_t op = nullptr;
+    cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
+    cublasLtMatmulAlgo_t algo;
+};
+Chosen g_chosen;
+cublasLtHandle_t g_handle = nullptr;
+void* g_workspace = nullptr;
+const size_t kWorkspaceBytes = 64ull << 20;
 }
 
 extern "C" {
@@ -29,12 +42,17 @@ int b200fp8_cmp_cublaslt(int m, int k, int n, const void* a, int a_dtype, const 
                          int iters, int max_algos, int fast_accum, float* best_ms, int* algos_found, void* stream_v)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    static cublasLtHandle_t handle = nullptr;
-    static void* workspace = nullptr;
-    const size_t ws_bytes = 64ull << 20;
-    if (!handle) {
-        if (cublasLtCreate(&handle) != CUBLAS_STATUS_SUCCESS) return 1001;
-        if (cudaMalloc(&workspace, ws_bytes) != cudaSuccess) return 1002;
+    const size_t ws_bytes = kWorkspaceBytes;
+    if (!g_handle) {
+        if (cublasLtCreate(&g_handle) != CUBLAS_STATUS_SUCCESS) return 1001;
+        if (cudaMalloc(&g_workspace, ws_bytes) != cudaSuccess) return 1002;
+    }
+    cublasLtHandle_t handle = g_handle;
+    void* workspace = g_workspace;
+    if (g_chosen.valid) {
+        cublasLtMatrixLayoutDestroy(g_chosen.la); cublasLtMatrixLayoutDestroy(g_chosen.lb);
+        cublasLtMatrixLayoutDestroy(g_chosen.lc); cublasLtMatmulDescDestroy(g_chosen.op);
+        g_chosen.valid = false;
     }
     cublasLtMatmulDesc_t op = nullptr;
     cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
@@ -85,6 +103,12 @@ int b200fp8_cmp_cublaslt(int m, int k, int n, const void* a, int a_dtype, const 
     // leave the fastest candidate's output in c
     cublasLtMatmul(handle, op, &alpha, b, la, a, lb, &beta, c, lc, c, lc, &res[best_i].algo, workspace, ws_bytes, stream);
     if (cudaStreamSynchronize(stream) != cudaSuccess) rc = 1004;
+    if (rc == 0) {
+        g_chosen.valid = true;
+        g_chosen.m = m; g_chosen.k = k; g_chosen.n = n; g_chosen.a_dtype = a_dtype; g_chosen.b_dtype = b_dtype;
+        g_chosen.op = op; g_chosen.la = la; g_chosen.lb = lb; g_chosen.lc = lc; g_chosen.algo = res[best_i].algo;
+        op = nullptr; la = lb = lc = nullptr;      // ownership moved
+    }
 done:
 #undef LT
     if (best_ms) *best_ms = best;
@@ -96,6 +120,33 @@ done:
     if (lb) cublasLtMatrixLayoutDestroy(lb);
     if (lc) cublasLtMatrixLayoutDestroy(lc);
     if (op) cublasLtMatmulDescDestroy(op);
+    return rc;
+}
+
+// Times `iters` back-to-back launches of the candidate chosen by the last b200fp8_cmp_cublaslt call
+// (same shape and dtypes required; returns -2 otherwise).  No selection, no warm-up: for alternating
+// comparisons under identical thermal conditions.
+int b200fp8_cmp_cublaslt_run(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype, float* c,
+                             int iters, float* mean_ms, void* stream_v)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const Chosen& ch = g_chosen;
+    if (!ch.valid || ch.m != m || ch.k != k || ch.n != n || ch.a_dtype != a_dtype || ch.b_dtype != b_dtype) return -2;
+    const float alpha = 1.0f, beta = 0.0f;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, stream);
+    for (int it = 0; it < iters; ++it)
+        cublasLtMatmul(g_handle, ch.op, &alpha, b, ch.la, a, ch.lb, &beta, c, ch.lc, c, ch.lc, &ch.algo, g_workspace,
+                       kWorkspaceBytes, stream);
+    cudaEventRecord(e1, stream);
+    int rc = cudaEventSynchronize(e1) == cudaSuccess ? 0 : 1003;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (mean_ms) *mean_ms = ms / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
     return rc;
 }
 
