@@ -285,7 +285,7 @@ def main() -> int:
                 "peak_source": peaks["source"] + ": 2 x sustained cuBLAS bf16 (fp8 issues at twice the bf16 rate)",
                 "frac_of_burst_peak": ach / (2.0 * peaks["bf16_burst"]),
                 "frac_of_nominal_4500": ach / NOMINAL_FP8_TFLOPS}
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None   # captured at N = 1
     roof["algorithmic_bytes"] = bytes_launch
     roof["algorithmic_flops"] = flops_launch
     roof["kernel_ms"] = avg_launch_ms

@@ -295,12 +295,17 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     float* dc = static_cast<float*>(ctx->host_c);
     const uint8_t* db = static_cast<const uint8_t*>(ctx->host_b);
 
-    // Column blocks of B / C: upload block j+1 and download block j-1 while block j computes.
+    // Pipeline over blocks of C so that uploads, the operator and the download of C overlap on three
+    // streams.  The smaller operand goes up whole first; the other one is streamed block by block:
+    //   n <= m : B first, then row blocks of A -> row blocks of C (contiguous downloads)
+    //   n >  m : A first, then column blocks of B / C (what a wide, short problem wants)
+    const bool by_rows = n <= m;
+    const int extent = by_rows ? m : n;
     int blocks = 1;
-    if (static_cast<double>(m) * n * k > 1e11 && n >= 2048) blocks = 8;
-    int nb = ((n + blocks - 1) / blocks + 255) / 256 * 256;
-    if (nb <= 0) nb = n;
-    blocks = (n + nb - 1) / nb;
+    if (static_cast<double>(m) * n * k > 1e11 && extent >= 2048) blocks = 8;
+    int step = ((extent + blocks - 1) / blocks + 255) / 256 * 256;
+    if (step <= 0) step = extent;
+    blocks = (extent + step - 1) / step;
     constexpr int kMaxBlocks = 64;
     if (blocks > kMaxBlocks) return cudaErrorInvalidValue;
     cudaEvent_t up[kMaxBlocks], done[kMaxBlocks];
@@ -313,20 +318,37 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     opt.depth = depth;
     cudaError_t first = cudaSuccess;
     auto keep = [&](cudaError_t x) { if (first == cudaSuccess && x != cudaSuccess) first = x; };
-    if (a_bytes) keep(cudaMemcpyAsync(ctx->host_a, a_host, a_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    uint8_t* da = static_cast<uint8_t*>(ctx->host_a);
+    const uint8_t* ha = static_cast<const uint8_t*>(a_host);
+    const uint8_t* hb = static_cast<const uint8_t*>(b_host);
+    if (by_rows) {
+        if (b_bytes) keep(cudaMemcpyAsync(ctx->host_b, hb, b_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    } else {
+        if (a_bytes) keep(cudaMemcpyAsync(da, ha, a_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
+    }
     for (int j = 0; j < blocks && first == cudaSuccess; ++j) {
-        const int n0 = j * nb, nn = (n - n0 < nb) ? n - n0 : nb;
-        if (k) keep(cudaMemcpyAsync(const_cast<uint8_t*>(db) + static_cast<size_t>(n0) * k,
-                                    static_cast<const uint8_t*>(b_host) + static_cast<size_t>(n0) * k,
-                                    static_cast<size_t>(nn) * k, cudaMemcpyHostToDevice, ctx->copy_in));
+        const int x0 = j * step, xx = (extent - x0 < step) ? extent - x0 : step;
+        const size_t off = static_cast<size_t>(x0) * k;
+        if (k) {
+            if (by_rows) keep(cudaMemcpyAsync(da + off, ha + off, static_cast<size_t>(xx) * k, cudaMemcpyHostToDevice, ctx->copy_in));
+            else keep(cudaMemcpyAsync(const_cast<uint8_t*>(db) + off, hb + off, static_cast<size_t>(xx) * k, cudaMemcpyHostToDevice, ctx->copy_in));
+        }
         keep(cudaEventRecord(up[j], ctx->copy_in));
         keep(cudaStreamWaitEvent(ctx->compute, up[j], 0));
-        keep(gemm_dispatch(m, k, nn, ctx->host_a, a_dtype, k, db + static_cast<size_t>(n0) * k, b_dtype, k, dc + n0, n,
-                           &opt, ctx->compute));
-        keep(cudaEventRecord(done[j], ctx->compute));
-        keep(cudaStreamWaitEvent(ctx->copy_out, done[j], 0));
-        keep(cudaMemcpy2DAsync(c_host + n0, static_cast<size_t>(n) * 4, dc + n0, static_cast<size_t>(n) * 4,
-                               static_cast<size_t>(nn) * 4, m, cudaMemcpyDeviceToHost, ctx->copy_out));
+        if (by_rows) {
+            float* cblk = dc + static_cast<size_t>(x0) * n;
+            keep(gemm_dispatch(xx, k, n, da + off, a_dtype, k, db, b_dtype, k, cblk, n, &opt, ctx->compute));
+            keep(cudaEventRecord(done[j], ctx->compute));
+            keep(cudaStreamWaitEvent(ctx->copy_out, done[j], 0));
+            keep(cudaMemcpyAsync(c_host + static_cast<size_t>(x0) * n, cblk, static_cast<size_t>(xx) * n * 4,
+                                 cudaMemcpyDeviceToHost, ctx->copy_out));
+        } else {
+            keep(gemm_dispatch(m, k, xx, da, a_dtype, k, db + off, b_dtype, k, dc + x0, n, &opt, ctx->compute));
+            keep(cudaEventRecord(done[j], ctx->compute));
+            keep(cudaStreamWaitEvent(ctx->copy_out, done[j], 0));
+            keep(cudaMemcpy2DAsync(c_host + x0, static_cast<size_t>(n) * 4, dc + x0, static_cast<size_t>(n) * 4,
+                                   static_cast<size_t>(xx) * 4, m, cudaMemcpyDeviceToHost, ctx->copy_out));
+        }
     }
     keep(cudaStreamSynchronize(ctx->copy_in));
     keep(cudaStreamSynchronize(ctx->compute));

@@ -9,9 +9,12 @@
 //   warp 1      TMEM allocation; one lane issues tcgen05.mma kind::f8f6f4 (four K=32
 //               instructions per k-block) into one of two TMEM accumulator buffers and
 //               commits to the ring's empty barriers / the accumulator's full barrier
-//   warps 2-5   epilogue: tcgen05.ld 32 rows x 32 columns at a time, stage through swizzled
-//               shared memory, TMA-store 32x32 FP32 boxes (hardware clips ragged M/N edges);
-//               runs concurrently with the next tile's main loop (double-buffered TMEM)
+//   warps 2-9   epilogue, two groups of four warps (a warp may only read its own quarter of the
+//               TMEM lanes): tcgen05.ld 32 rows x 32 columns at a time, software-pipelined against
+//               the stores, staged through swizzled shared memory, TMA-stored as 32x32 FP32 boxes
+//               (hardware clips ragged M/N edges); runs concurrently with the next tile's main
+//               loop (two TMEM accumulator slots).  With one accumulator per tile the groups
+//               split its columns; with two (NACC == 2) each group drains one of them
 // CTAS == 2 pairs two CTAs of a cluster on a 256 x BN tile (cta_group::2): each CTA loads
 // its own 128 rows of A and its own half of the B tile (no multicast), the leader CTA
 // issues the MMAs for both, and each CTA drains its own 128 accumulator rows.
@@ -62,7 +65,7 @@ enum : int {
 
 constexpr int kBlockK = 128;         // bytes (= FP8 elements) of K per ring slot: one swizzle-128B row
 constexpr int kTileM = 128;          // accumulator rows per CTA = TMEM lanes
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;          // two groups of four (one warp per TMEM lane quarter in each group)
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
@@ -110,7 +113,7 @@ struct GemmSmem {
     static constexpr int kStageBytes = kABytes + NACC * kBBytes;
     static constexpr int kTxBytes = kStageBytes * CTAS;      // bytes landing per ring slot across the pair
     static constexpr int kEpiBufBytes = 32 * 32 * 4;         // one 32x32 FP32 box
-    static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBufBytes;
+    static constexpr int kEpiBytes = kEpiWarps * kEpiBufBytes;   // one staging box per epilogue warp
     static constexpr int kRingOff = 0;
     static constexpr int kEpiOff = STAGES * kStageBytes;
     static constexpr int kBarOff = kEpiOff + kEpiBytes;      // full[STAGES] empty[STAGES] tfull[2] tempty[2]
@@ -157,7 +160,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(bar_tfull + 8 * b, 1);
-            ptx::mbar_init(bar_tempty + 8 * b, kEpiWarps * CTAS);
+            ptx::mbar_init(bar_tempty + 8 * b, (kEpiWarps / NACC) * CTAS);   // warps that drain one slot, in all CTAs
         }
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_a);
@@ -339,65 +342,74 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else {
         // ---------------- epilogue warps ----------------
         const int q = warp & 3;                                   // TMEM lane quarter this warp may read
-        const uint32_t stage_base = smem_base + L::kEpiOff + q * (2 * L::kEpiBufBytes);
+        const int grp = (warp - 2) >> 2;                          // 0 or 1
+        const uint32_t sb = smem_base + L::kEpiOff + (warp - 2) * L::kEpiBufBytes;   // this warp's staging box
         const uint32_t tempty0 = pair ? ptx::mapa(bar_tempty, 0) : bar_tempty;
         const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
+        constexpr int kChunks = BN / 32 / (NACC == 1 ? 2 : 1);    // 32-column chunks this warp drains per tile
         int it = 0;
-        bool ok = true;
-        for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
+        for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
             int m0, n0;
             tile_coords(t, m0, n0);
             const int row0 = m0 + q * 32;
-#pragma unroll 1
-            for (int j = 0; j < NACC; ++j) {
-                const int slot = slot_of(it, j);
-                if (!wait_bounded(bar_tfull + 8 * slot, use_parity(it), abort_flag, pair, args.wait_hint_ns)) {
-                    record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
-                    ok = false;
-                    break;
+            const int slot = slot_of(it, grp);                    // NACC == 1: both groups share the tile's slot
+            const int c_first = (NACC == 1) ? grp * kChunks : 0;
+            if (!wait_bounded(bar_tfull + 8 * slot, use_parity(it), abort_flag, pair, args.wait_hint_ns)) {
+                record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
+                break;
+            }
+            __syncwarp();
+            ptx::tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN + c_first * 32;
+            const int col_base = n0 + (NACC == 2 ? grp * BN : 0) + c_first * 32;
+
+            // one chunk: registers -> swizzled staging box -> TMA store (or plain stores when C is not TMA-able)
+            auto emit = [&](const uint32_t (&v)[32], int c) {
+                const int col0 = col_base + c * 32;
+                if (args.tma_store) {
+                    if (issuer) ptx::bulk_wait_group_read<0>();   // the previous store has finished reading the box
+                    __syncwarp();
+                    const uint32_t row_addr = sb + lane * 128;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        ptx::st_shared_v4(row_addr + ((i ^ (lane & 7)) << 4), v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (issuer) {
+                        if (row0 < args.M && col0 < args.N && !(args.debug & 2)) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        ptx::bulk_commit_group();
+                    }
+                } else {
+                    const int row = row0 + lane;
+                    if (row < args.M) {
+                        float* dst = args.C + static_cast<long long>(row) * args.ldc + col0;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.N) dst[i] = __uint_as_float(v[i]);
+                    }
                 }
+            };
+            auto release_slot = [&]() {                           // accumulator columns of this warp are in registers
+                ptx::tc_fence_before();
                 __syncwarp();
-                ptx::tc_fence_after();
-                const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t v[32];
-                    ptx::tmem_ld_32x32(t_addr + c * 32, v);
-                    ptx::tmem_ld_wait();
-                    if (c == BN / 32 - 1) {
-                        // slot fully read: hand it back to the MMA warp
-                        ptx::tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (pair) ptx::mbar_arrive_cluster(tempty0 + 8 * slot);
-                            else ptx::mbar_arrive(bar_tempty + 8 * slot);
-                        }
-                    }
-                    const int col0 = n0 + j * BN + c * 32;
-                    if (args.tma_store) {
-                        const uint32_t sb = stage_base + (c & 1) * L::kEpiBufBytes;
-                        if (issuer) ptx::bulk_wait_group_read<1>();    // the store that last used this buffer has read it
-                        __syncwarp();
-                        const uint32_t row_addr = sb + lane * 128;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            ptx::st_shared_v4(row_addr + ((i ^ (lane & 7)) << 4), v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                        ptx::fence_proxy_async_smem();
-                        __syncwarp();
-                        if (issuer) {
-                            if (row0 < args.M && col0 < args.N && !(args.debug & 2)) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
-                            ptx::bulk_commit_group();
-                        }
-                    } else {
-                        const int row = row0 + lane;
-                        if (row < args.M) {
-                            float* dst = args.C + static_cast<long long>(row) * args.ldc + col0;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (col0 + i < args.N) dst[i] = __uint_as_float(v[i]);
-                        }
-                    }
+                if (lane == 0) {
+                    if (pair) ptx::mbar_arrive_cluster(tempty0 + 8 * slot);
+                    else ptx::mbar_arrive(bar_tempty + 8 * slot);
                 }
+            };
+
+            // two register sets: the TMEM load of chunk c+1 is in flight while chunk c is stored
+            uint32_t va[32], vb[32];
+            ptx::tmem_ld_32x32(t_addr, va);
+#pragma unroll 1
+            for (int c = 0; c < kChunks; c += 2) {
+                ptx::tmem_ld_wait();                              // va = chunk c
+                ptx::tmem_ld_32x32(t_addr + (c + 1) * 32, vb);    // kChunks is even: chunk c+1 exists
+                emit(va, c);
+                ptx::tmem_ld_wait();                              // vb = chunk c+1
+                if (c + 2 < kChunks) ptx::tmem_ld_32x32(t_addr + (c + 2) * 32, va);
+                else release_slot();
+                emit(vb, c + 1);
             }
         }
         if (issuer) ptx::bulk_wait_group<0>();                    // all stores of this warp are complete

@@ -329,7 +329,7 @@ def test_config5_full_size_one_rank_shard(g, oracle):
 
 # ---------------------------------------------------------------- host-pointer entry point, generator, drop-in binary
 
-@pytest.mark.parametrize("shape", [(300, 272, 520), (64, 1024, 512), (2048, 2048, 4096)])
+@pytest.mark.parametrize("shape", [(300, 272, 520), (64, 1024, 512), (2048, 2048, 4096), (8192, 4096, 4096), (4096, 4096, 8192)])
 def test_host_entry_point_matches_device_entry(g, oracle, shape):
     m, k, n = shape
     a, b = random_operands(g, m, k, n, 0, 1, seed=23)
