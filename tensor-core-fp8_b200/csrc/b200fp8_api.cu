@@ -96,7 +96,9 @@ struct Tune {
     int debug = 0;
     int pace_min_waves = 8;       // tile pacing only pays on long runs
     int pace_limit_ns = 30000;
+    int store_gap_ns = 0;
     Tune() {
+        if (const char* v = getenv("B200FP8_STORE_GAP_NS")) store_gap_ns = atoi(v);
         if (const char* v = getenv("B200FP8_PACE_MIN_WAVES")) pace_min_waves = atoi(v);
         if (const char* v = getenv("B200FP8_PACE_LIMIT_NS")) pace_limit_ns = atoi(v);
         if (const char* v = getenv("B200FP8_DEBUG")) debug = atoi(v);
@@ -130,6 +132,7 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     args.group_m = (CTAS == 2) ? tune().group_m_pair : tune().group_m_single;
     args.wait_hint_ns = static_cast<uint32_t>(tune().wait_hint_ns);
     args.debug = tune().debug;
+    args.store_gap_ns = (NACC == 1) ? static_cast<unsigned int>(tune().store_gap_ns) : 0u;
     if (args.debug & (64 | 128)) {
         if (!g_trace) { cudaMalloc(&g_trace, 3 * 4096 * sizeof(long long)); cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long)); }
         args.trace = g_trace;

@@ -52,6 +52,7 @@ struct GemmArgs {
     int* status;          // device status word: 0 = ok, else first error code recorded
     unsigned int* pace;   // tile-pacing counter (zero at launch) or nullptr: see the producer warp
     unsigned int pace_limit_ns;
+    unsigned int store_gap_ns;   // pause between an epilogue warp's chunk stores (spreads C writes over the next main loop)
     long long* trace;     // diagnostics (debug & 64): per k-block clock64 stamps of CTA 0's MMA thread
 };
 
@@ -409,7 +410,9 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 ptx::tmem_ld_wait();                              // vb = chunk c+1
                 if (c + 2 < kChunks) ptx::tmem_ld_32x32(t_addr + (c + 2) * 32, va);
                 else release_slot();
+                if (args.store_gap_ns) __nanosleep(args.store_gap_ns);
                 emit(vb, c + 1);
+                if (args.store_gap_ns && c + 2 < kChunks) __nanosleep(args.store_gap_ns);
             }
         }
         if (issuer) ptx::bulk_wait_group<0>();                    // all stores of this warp are complete
