@@ -150,4 +150,16 @@ int b200fp8_cmp_cublaslt_run(int m, int k, int n, const void* a, int a_dtype, co
     return rc;
 }
 
+// Enqueues ONE launch of the chosen candidate on `stream` and returns without synchronising, so that a
+// caller can time batches over rotating buffers exactly as it times the library's own calls.
+int b200fp8_cmp_cublaslt_enqueue(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype, float* c,
+                                 void* stream_v)
+{
+    const Chosen& ch = g_chosen;
+    if (!ch.valid || ch.m != m || ch.k != k || ch.n != n || ch.a_dtype != a_dtype || ch.b_dtype != b_dtype) return -2;
+    const float alpha = 1.0f, beta = 0.0f;
+    return cublasLtMatmul(g_handle, ch.op, &alpha, b, ch.la, a, ch.lb, &beta, c, ch.lc, c, ch.lc, &ch.algo, g_workspace,
+                          kWorkspaceBytes, static_cast<cudaStream_t>(stream_v)) == CUBLAS_STATUS_SUCCESS ? 0 : 2001;
+}
+
 }  // extern "C"
