@@ -39,7 +39,12 @@ WORKLOADS = {
     "gemm4096": (4096, 4096, 4096, False),
     "ffn_up": (8192, 8192, 28672, False),
     "ffn_down": (8192, 28672, 8192, False),
+    "gemm1024": (1024, 1024, 1024, False),
+    "skinny1": (1, 8192, 8192, False),
     "skinny16": (16, 8192, 8192, False),
+    "skinny64": (64, 8192, 8192, False),
+    "skinny128": (128, 8192, 8192, False),
+    "skinny_wide": (32, 8192, 57344, False),
 }
 SEED_BASE = 0xB200F800
 NOMINAL_FP8_TFLOPS = 4500.0
@@ -187,6 +192,8 @@ def main() -> int:
     ap.add_argument("--allgather", action="store_true", help="also time an NCCL all-gather of the C shards (N > 1)")
     ap.add_argument("--kernel", type=int, default=0)
     ap.add_argument("--depth", type=int, default=0)
+    ap.add_argument("--a-dtype", default="e4m3", choices=["e4m3", "e5m2"])
+    ap.add_argument("--b-dtype", default="e4m3", choices=["e4m3", "e5m2"])
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -216,17 +223,20 @@ def main() -> int:
     sh = shard_mod.column_shard(N, rank, world) if sharded else shard_mod.Shard(rank, world, 0, N)
     n_local = sh.n
     seed_a, seed_b = SEED_BASE + 64, SEED_BASE + 65
+    f8_of = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+    fa, fb = f8_of[args.a_dtype], f8_of[args.b_dtype]
+    sig_a, sig_b = (1.0 if args.a_dtype == "e4m3" else 2.0), (1.0 if args.b_dtype == "e4m3" else 2.0)
     f8 = torch.float8_e4m3fn
 
     # operands: several B (and C) buffers for small workloads so that every step reads from HBM, not L2
     bytes_per_set = n_local * K + 4 * M * n_local
     nsets = 1 if (M * K + bytes_per_set) > (512 << 20) else max(2, min(8, (1 << 30) // max(1, bytes_per_set)))
-    a = torch.empty((M, K), dtype=f8, device=dev)
-    g.fill_normal(a, 1.0, seed_a)
+    a = torch.empty((M, K), dtype=fa, device=dev)
+    g.fill_normal(a, sig_a, seed_a)
     bs, cs = [], []
     for i in range(nsets):
-        b = torch.empty((n_local, K), dtype=f8, device=dev)
-        g.fill_normal(b, 1.0, seed_b + 1000 * i, index_offset=sh.n_begin * K)
+        b = torch.empty((n_local, K), dtype=fb, device=dev)
+        g.fill_normal(b, sig_b, seed_b + 1000 * i, index_offset=sh.n_begin * K)
         bs.append(b)
         cs.append(torch.empty((M, n_local), dtype=torch.float32, device=dev))
     torch.cuda.synchronize()
@@ -243,18 +253,39 @@ def main() -> int:
     for i in range(args.warmup):
         step(i)
     barrier()
+    # Short steps are launch-bound when driven call by call from Python, so their K steps are captured
+    # once in a CUDA graph and replayed; long steps are timed launch by launch.
+    use_graph = 2.0 * M * K * n_local < 2e12
     launches0 = g.launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    with ClockSampler(physical_gpu_index(local_rank)) as clk:
-        ev[0].record()
-        for i in range(args.steps):
-            step(i)
-            ev[i + 1].record()
-        torch.cuda.synchronize()
-    launches = g.launch_count() - launches0
-    barrier()
-    total_ms = ev[0].elapsed_time(ev[-1])
-    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(args.steps):
+                step(i)
+        launches = g.launch_count() - launches0          # kernel nodes in the graph = launches per replay
+        graph.replay()
+        barrier()
+        e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(physical_gpu_index(local_rank)) as clk:
+            e_beg.record()
+            graph.replay()
+            e_end.record()
+            torch.cuda.synchronize()
+        barrier()
+        total_ms = e_beg.elapsed_time(e_end)
+        per_launch_ms = [total_ms / args.steps] * args.steps
+    else:
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        with ClockSampler(physical_gpu_index(local_rank)) as clk:
+            ev[0].record()
+            for i in range(args.steps):
+                step(i)
+                ev[i + 1].record()
+            torch.cuda.synchronize()
+        launches = g.launch_count() - launches0
+        barrier()
+        total_ms = ev[0].elapsed_time(ev[-1])
+        per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     if g.device_status() != 0:
         raise SystemExit("device status word is non-zero: a kernel's bounded wait ran out")
     t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
@@ -295,17 +326,18 @@ def main() -> int:
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
         "config": {"workload": args.workload, "M": M, "K": K, "N": N, "n_per_rank": n_local, "layout": "row-col",
-                   "a": "e4m3", "b": "e4m3", "out": "f32", "parallelism": f"n-shard x{world}" if sharded else f"replicas x{world}",
+                   "a": args.a_dtype, "b": args.b_dtype, "out": "f32", "parallelism": f"n-shard x{world}" if sharded else f"replicas x{world}",
                    "l2": "inputs larger than L2" if nsets == 1 else f"rotating over {nsets} distinct B/C buffer sets larger than L2",
-                   "kernel": args.kernel, "depth": args.depth},
+                   "kernel": args.kernel, "depth": args.depth,
+                   "timing": "one CUDA graph of all steps, replayed" if use_graph else "launch by launch"},
         "roofline": roof, "gpu_launches": int(launches), "clocks": clk.summary(),
         "pct_of_nominal_fp8_peak": 100.0 * value / (NOMINAL_FP8_TFLOPS * world),
     }
 
     # ---- end to end through the host-pointer entry point (pinned host buffers) ----
     if not args.no_e2e:
-        ha = torch.empty((M, K), dtype=torch.uint8).pin_memory().view(f8)
-        hb = torch.empty((n_local, K), dtype=torch.uint8).pin_memory().view(f8)
+        ha = torch.empty((M, K), dtype=torch.uint8).pin_memory().view(fa)
+        hb = torch.empty((n_local, K), dtype=torch.uint8).pin_memory().view(fb)
         hc = torch.empty((M, n_local), dtype=torch.float32).pin_memory()
         ha.view(torch.uint8).copy_(a.view(torch.uint8))
         hb.view(torch.uint8).copy_(bs[0].view(torch.uint8))
@@ -373,21 +405,33 @@ def main() -> int:
             if cmp is not None:
                 ms = ctypes.c_float(-1)
                 found = ci(0)
-                have_cmp = cmp.b200fp8_cmp_cublaslt(m2, k2, n2, a2.data_ptr(), 0, b2.data_ptr(), 0, c2.data_ptr(), 3, 8, 0,
+                have_cmp = cmp.b200fp8_cmp_cublaslt(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), b2.data_ptr(), g.dtype_code(b2), c2.data_ptr(), 3, 8, 0,
                                                     ctypes.byref(ms), ctypes.byref(found), stream) == 0
             ours, theirs = [], []
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            side_graph = None
+            if fl < 2e12:                                 # same launch-overhead treatment as the main loop
+                for _ in range(2):
+                    g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+                torch.cuda.synchronize()
+                side_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(side_graph):
+                    for _ in range(iters):
+                        g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
             for rnd in range(4):
                 e0.record()
-                for _ in range(iters):
-                    g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+                if side_graph is not None:
+                    side_graph.replay()
+                else:
+                    for _ in range(iters):
+                        g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
                 e1.record()
                 torch.cuda.synchronize()
                 if rnd:                                   # round 0 warms both up
                     ours.append(e0.elapsed_time(e1) / iters)
                 if have_cmp:
                     ms = ctypes.c_float(-1)
-                    cmp.b200fp8_cmp_cublaslt_run(m2, k2, n2, a2.data_ptr(), 0, b2.data_ptr(), 0, c2.data_ptr(), iters,
+                    cmp.b200fp8_cmp_cublaslt_run(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), b2.data_ptr(), g.dtype_code(b2), c2.data_ptr(), iters,
                                                  ctypes.byref(ms), stream)
                     if rnd:
                         theirs.append(ms.value)
