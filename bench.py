@@ -190,6 +190,8 @@ def main() -> int:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the cuBLASLt / 8192^3 side measurements")
     ap.add_argument("--allgather", action="store_true", help="also time an NCCL all-gather of the C shards (N > 1)")
+    ap.add_argument("--fused-allgather", action="store_true",
+                    help="also time the GEMM with the all-gather fused into its epilogue (N > 1): every rank ends with all of C")
     ap.add_argument("--kernel", type=int, default=0)
     ap.add_argument("--depth", type=int, default=0)
     ap.add_argument("--a-dtype", default="e4m3", choices=["e4m3", "e5m2"])
@@ -374,6 +376,30 @@ def main() -> int:
         line["allgather"] = {"ms": float(tg.item()), "bytes_received_per_rank": int(4 * M * n_local * (world - 1)),
                              "layout": "[rank][M][N/R] blocks"}
         del full
+
+    # ---- the same step with the all-gather of C fused into the kernel's epilogue (peer stores over NVLink) ----
+    if args.fused_allgather and world > 1 and sharded:
+        shared = shard_mod.SharedC(M, N, dev)
+        fsteps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(fsteps):
+            shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        tf = torch.tensor([e0.elapsed_time(e1) / fsteps], dtype=torch.float64, device=dev)
+        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+        fms = float(tf.item())
+        line["fused_allgather"] = {"ms_per_step": fms, "tflops": 2.0 * M * K * N / (fms * 1e-3) / 1e12, "steps": fsteps,
+                                   "nvlink_bytes_sent_per_rank": int(4 * M * n_local * (world - 1)),
+                                   "result": "every rank holds the full row-major C; no separate collective, no re-layout"}
+        if g.device_status() != 0:
+            raise SystemExit("device status word is non-zero after the fused run")
+        shared.close()
 
     # ---- side measurements on rank 0 at N = 1: the 8192^3 target shape and the bench workload, ours against
     #      cuBLASLt on the same buffers, ALTERNATING so that both see the same clocks and temperature ----

@@ -77,6 +77,26 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
                                void* stream);
 
 /*
+ * N-sharded multi-GPU GEMM with the all-gather of C fused into the kernel's
+ * epilogue (no counterpart in the reference, which is single-GPU; it follows
+ * the operator above).  Rank `rank` of `world` (<= 8, one process per GPU)
+ * owns rows [n_begin, n_begin + n_local) of B -- `b_shard` points at them --
+ * and computes the matching column block of C.  `c_all` is a HOST array of
+ * `world` DEVICE pointers: the full M x n_total matrix C of every rank, own
+ * included; the other ranks' matrices must be mapped into this process (CUDA
+ * IPC, peer access enabled).  Every finished 32x32 box of the block is stored
+ * to the own matrix and, with plain 16-byte stores over NVLink, to the same
+ * position of every peer's matrix, so that after all ranks' kernels have
+ * finished each rank holds the complete row-major C: no separate collective
+ * and no re-layout pass.  Requirements on top of the operator's: n_total and
+ * n_begin multiples of 4, every C base 16-byte aligned.  The caller
+ * synchronises the ranks (stream sync + barrier) before reading C.
+ */
+int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,
+                                      int b_dtype, float* const* c_all, int world, int rank, long long n_total,
+                                      long long n_begin, const b200fp8_options* options, void* stream);
+
+/*
  * The whole call sequence of the reference's benchmark driver for one GEMM
  * (BmFN, GEMM/gemm_main.cpp:56-64 upload, :77 / :123 operator call, :161
  * download) with HOST pointers: uploads A and B, runs the operator, downloads
@@ -137,6 +157,23 @@ int b200fp8_device_status(int* status, int reset);
  */
 int b200fp8_gemm_rowcol_f32_noalloc(int m, int k, int n, const void* a, int a_dtype, const void* b, int b_dtype,
                                     float* c, int* status_word, void* stream);
+
+/*
+ * Lets kernels on the current device store into memory of `peer_device` (needed once per
+ * peer before b200fp8_gemm_rowcol_f32_allgather; already-enabled counts as success).
+ */
+int b200fp8_enable_peer_access(int peer_device);
+
+/*
+ * Device memory that other processes on the same node can map (CUDA IPC), for the C matrices of
+ * b200fp8_gemm_rowcol_f32_allgather.  The owner allocates and gets a 64-byte handle to hand to its
+ * peers (any transport); a peer opens it WITH ITS OWN DEVICE CURRENT, which maps the memory for that
+ * device and enables peer access as needed, and closes it before the owner frees.
+ */
+int b200fp8_ipc_alloc(size_t bytes, void** device_ptr, unsigned char handle[64]);
+int b200fp8_ipc_open(const unsigned char handle[64], void** device_ptr);
+int b200fp8_ipc_close(void* device_ptr);
+int b200fp8_ipc_free(void* device_ptr);
 
 /* Number of this library's kernels launched by the calling thread so far. */
 long long b200fp8_launch_count(void);

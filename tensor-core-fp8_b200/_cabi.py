@@ -27,10 +27,16 @@ CMP_LIB_PATH = os.path.join(CSRC, "libb200fp8_cmp.so")
 DECLARED_SYMBOLS = (
     "b200fp8_gemm_rowcol_f32",
     "b200fp8_gemm_rowcol_f32_ex",
+    "b200fp8_gemm_rowcol_f32_allgather",
     "b200fp8_gemm_rowcol_f32_host",
     "b200fp8_gemm_rowcol_f32_noalloc",
     "b200fp8_fill_normal",
     "b200fp8_device_status",
+    "b200fp8_enable_peer_access",
+    "b200fp8_ipc_alloc",
+    "b200fp8_ipc_open",
+    "b200fp8_ipc_close",
+    "b200fp8_ipc_free",
     "b200fp8_launch_count",
     "b200fp8_version",
 )
@@ -71,9 +77,16 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_gemm_rowcol_f32.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp]
         L.b200fp8_gemm_rowcol_f32_ex.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ll,
                                                  ctypes.POINTER(Options), vp]
+        L.b200fp8_gemm_rowcol_f32_allgather.argtypes = [ci, ci, ci, vp, ci, vp, ci, ctypes.POINTER(vp), ci, ci, ll, ll,
+                                                        ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
         L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
         L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]
+        L.b200fp8_enable_peer_access.argtypes = [ci]
+        L.b200fp8_ipc_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
+        L.b200fp8_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.b200fp8_ipc_close.argtypes = [vp]
+        L.b200fp8_ipc_free.argtypes = [vp]
         L.b200fp8_device_status.argtypes = [ctypes.POINTER(ci), ci]
         L.b200fp8_launch_count.restype = ll
         L.b200fp8_version.restype = ctypes.c_char_p

@@ -88,6 +88,12 @@ cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// Destinations of the fused all-gather epilogue: this rank's column block inside every peer's C.
+struct PeerSet {
+    int count = 0;
+    float* c[kMaxPeers] = {};
+};
+
 // Tuning knobs read once from the environment (B200FP8_*); defaults are the measured best.
 struct Tune {
     int wait_hint_ns = 0;
@@ -113,7 +119,7 @@ long long* g_trace = nullptr;   // diagnostics buffer (B200FP8_DEBUG & 64)
 template <int BN, int STAGES, int CTAS, int NACC>
 cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
-                        cudaStream_t stream) {
+                        const PeerSet* peers, cudaStream_t stream) {
     using L = GemmSmem<BN, STAGES, CTAS, NACC>;
     static bool attr_done[kMaxDevices] = {};
     auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC>;
@@ -140,6 +146,11 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
     args.tma_store = ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
     args.C = c; args.ldc = ldc; args.status = ctx.status;
+    if (peers && peers->count > 0) {
+        if (!args.tma_store || (n % 4) != 0) return cudaErrorInvalidValue;     // peer stores move whole 16-byte groups
+        args.num_peers = peers->count;
+        for (int i = 0; i < peers->count; ++i) args.peer_c[i] = peers->c[i];
+    }
 
     CUtensorMap ta, tb, tc;
     cudaError_t e;
@@ -186,7 +197,8 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
 bool valid_dtype(int d) { return d == B200FP8_E4M3 || d == B200FP8_E5M2; }
 
 cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
-                          long long ldb, float* c, long long ldc, const b200fp8_options* opt, cudaStream_t stream) {
+                          long long ldb, float* c, long long ldc, const b200fp8_options* opt, cudaStream_t stream,
+                          const PeerSet* peers = nullptr) {
     if (m < 0 || n < 0 || k < 0 || !valid_dtype(a_dtype) || !valid_dtype(b_dtype)) return cudaErrorInvalidValue;
     if (m == 0 || n == 0) return cudaSuccess;
     if (!c || ldc < n) return cudaErrorInvalidValue;
@@ -221,10 +233,11 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
     if (kernel == B200FP8_KERNEL_SKINNY && m > kSkinnyMaxM) return cudaErrorInvalidValue;
+    if (peers && peers->count > 0 && kernel == B200FP8_KERNEL_SKINNY) kernel = B200FP8_KERNEL_PAIR_N256;
 
 #define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
 #define B200FP8_LAUNCH4(BN, ST, CT, NA) \
-    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, stream)
+    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, stream)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);
@@ -275,6 +288,21 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
                                void* stream) {
     if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
     return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, c, ldc, options, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,
+                                      int b_dtype, float* const* c_all, int world, int rank, long long n_total,
+                                      long long n_begin, const b200fp8_options* options, void* stream) {
+    if (world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world || !c_all) return cudaErrorInvalidValue;
+    if (n_begin < 0 || n_local < 0 || n_begin + n_local > n_total || (n_begin % 4) || (n_total % 4)) return cudaErrorInvalidValue;
+    if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
+    PeerSet peers;
+    for (int r = 0; r < world; ++r) {
+        if (!c_all[r] || (reinterpret_cast<uintptr_t>(c_all[r]) % 16)) return cudaErrorInvalidValue;
+        if (r != rank) peers.c[peers.count++] = c_all[r] + n_begin;
+    }
+    return gemm_dispatch(m, k, n_local, a, a_dtype, k, b_shard, b_dtype, k, c_all[rank] + n_begin, n_total, options,
+                         static_cast<cudaStream_t>(stream), &peers);
 }
 
 int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_dtype, const void* b_host, int b_dtype,
@@ -515,6 +543,42 @@ int b200fp8_device_status(int* status, int reset) {
     if (reset) e = cudaMemset(ctx->status, 0, sizeof(int));
     return e;
 }
+
+int b200fp8_enable_peer_access(int peer_device) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (peer_device == dev) return cudaSuccess;
+    int can = 0;
+    if ((e = cudaDeviceCanAccessPeer(&can, dev, peer_device)) != cudaSuccess) return e;
+    if (!can) return cudaErrorPeerAccessUnsupported;
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+    return e;
+}
+
+int b200fp8_ipc_alloc(size_t bytes, void** device_ptr, unsigned char handle[64]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!device_ptr || !handle || bytes == 0) return cudaErrorInvalidValue;
+    cudaError_t e = cudaMalloc(device_ptr, bytes);
+    if (e != cudaSuccess) return e;
+    cudaIpcMemHandle_t h;
+    if ((e = cudaIpcGetMemHandle(&h, *device_ptr)) != cudaSuccess) { cudaFree(*device_ptr); *device_ptr = nullptr; return e; }
+    memcpy(handle, &h, sizeof(h));
+    return cudaSuccess;
+}
+
+int b200fp8_ipc_open(const unsigned char handle[64], void** device_ptr) {
+    if (!device_ptr || !handle) return cudaErrorInvalidValue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    // opened with the IMPORTING device current: the mapping is made for this device, peer access enabled lazily
+    return cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+
+int b200fp8_ipc_close(void* device_ptr) { return device_ptr ? cudaIpcCloseMemHandle(device_ptr) : cudaSuccess; }
+
+int b200fp8_ipc_free(void* device_ptr) { return device_ptr ? cudaFree(device_ptr) : cudaSuccess; }
 
 long long b200fp8_launch_count(void) { return t_launches; }
 

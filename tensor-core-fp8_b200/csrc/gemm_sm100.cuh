@@ -36,6 +36,8 @@
 
 namespace b200fp8 {
 
+constexpr int kMaxPeers = 7;         // one box of 8 GPUs
+
 struct GemmArgs {
     int M, N, K;
     int num_k_blocks;     // ceil(K / 128)
@@ -54,6 +56,11 @@ struct GemmArgs {
     unsigned int pace_limit_ns;
     unsigned int store_gap_ns;   // pause between an epilogue warp's chunk stores (spreads C writes over the next main loop)
     long long* trace;     // diagnostics (debug & 64): per k-block clock64 stamps of CTA 0's MMA thread
+    // Fused all-gather of C (N-sharded multi-GPU run): every finished box is also stored, with plain
+    // 16-byte stores over NVLink, into the same position of the C matrix of each peer GPU.
+    // peer_c[p] points at this rank's column block inside peer p's full matrix (row pitch ldc).
+    int num_peers;
+    float* peer_c[kMaxPeers];
 };
 
 enum : int {
@@ -379,6 +386,29 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (issuer) {
                         if (row0 < args.M && col0 < args.N && !(args.debug & 2)) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
                         ptx::bulk_commit_group();
+                    }
+                    if (args.num_peers > 0) {
+                        // Read the box back row-contiguously (8 lanes cover one 128-byte row, 4 rows per
+                        // instruction) and push it to every peer: full 128-byte lines over NVLink.
+                        uint4 w[8];
+                        const int chunk = lane & 7;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = i * 4 + (lane >> 3);
+                            w[i] = ptx::ld_shared_v4(sb + r * 128 + ((chunk ^ (r & 7)) << 4));
+                        }
+                        const int col = col0 + chunk * 4;
+                        if (col < args.N) {                        // N % 4 == 0 on this path: whole 16-byte groups
+                            for (int p = 0; p < args.num_peers; ++p) {
+                                float* base = args.peer_c[p] + col;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    const int row = row0 + i * 4 + (lane >> 3);
+                                    if (row < args.M)
+                                        *reinterpret_cast<uint4*>(base + static_cast<long long>(row) * args.ldc) = w[i];
+                                }
+                            }
+                        }
                     }
                 } else {
                     const int row = row0 + lane;

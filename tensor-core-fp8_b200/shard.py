@@ -43,3 +43,99 @@ def gather_layout_to_row_major(blocks, m: int):
     """All-gather returns [R][M][N/R]; this is the index map back to row-major [M][N] (host-side check)."""
     import torch
     return torch.cat([b.reshape(m, -1) for b in blocks], dim=1)
+
+
+class _DevicePointer:
+    """Lets torch wrap a raw device pointer (``torch.as_tensor``) without owning it."""
+
+    def __init__(self, ptr: int, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+
+
+class SharedC:
+    """The full M x N matrix C of every rank, visible to every rank (one process per GPU, one node).
+
+    Each rank allocates its own full C through the library's CUDA-IPC helpers and hands the handle to
+    the others over `torch.distributed`; each rank opens its peers' handles with its own device current,
+    so the mappings (and peer access) belong to the device whose kernels will store through them.
+    `tensors[r]` is rank r's C as seen from this process.  Before first use the mapping is proven with
+    plain copies: every rank writes its rank number into one word of every matrix and checks its own.
+    Call `close()` (collective) when done.
+    """
+
+    def __init__(self, m: int, n_total: int, device, group=None):
+        import ctypes
+        import torch
+        import torch.distributed as dist
+        from . import _cabi
+        lib = _cabi.lib()
+        self._lib, self._group = lib, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("fused all-gather covers one box of at most 8 GPUs")
+        if n_total < self.world:
+            raise ValueError("need at least one column per rank")
+        self.device = torch.device(device)
+        self._ptrs = [None] * self.world
+        with torch.cuda.device(self.device):
+            own = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            _cabi.check(lib.b200fp8_ipc_alloc(m * n_total * 4, ctypes.byref(own), handle), "ipc_alloc")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self._ptrs[r] = own.value
+                else:
+                    p = ctypes.c_void_p()
+                    _cabi.check(lib.b200fp8_ipc_open(h, ctypes.byref(p)), f"ipc_open of rank {r}'s C")
+                    self._ptrs[r] = p.value
+            self.tensors = [torch.as_tensor(_DevicePointer(p, (m, n_total)), device=self.device) for p in self._ptrs]
+            self.own = self.tensors[self.rank]
+            # prove every mapping with copies (a bad mapping fails here with an error, not inside a kernel)
+            mark = torch.full((1,), float(self.rank + 1), dtype=torch.float32, device=self.device)
+            for t in self.tensors:
+                t[0, self.rank:self.rank + 1].copy_(mark)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=group)
+            seen = self.own[0, :self.world].cpu().tolist()
+            if seen != [float(r + 1) for r in range(self.world)]:
+                raise RuntimeError(f"peer mapping check failed on rank {self.rank}: {seen}")
+            dist.barrier(group=group)
+
+    def pointers(self):
+        import ctypes
+        return (ctypes.c_void_p * self.world)(*self._ptrs)
+
+    def close(self):
+        """Collective: unmap the peers' matrices, then free the own one."""
+        import torch
+        import torch.distributed as dist
+        if self._ptrs is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self._group)
+        self.tensors, self.own = None, None
+        with torch.cuda.device(self.device):
+            for r, p in enumerate(self._ptrs):
+                if r != self.rank:
+                    self._lib.b200fp8_ipc_close(p)
+            dist.barrier(group=self._group)
+            self._lib.b200fp8_ipc_free(self._ptrs[self.rank])
+        self._ptrs = None
+
+
+def gemm_allgather(a, b_shard, shared: "SharedC", shard: Shard, n_total: int, *, depth: int = 0, kernel: int = 0):
+    """This rank's column block of C = A B^T, written into every rank's full C by the kernel's epilogue."""
+    import ctypes
+    import torch
+    from . import _cabi
+    from .gemm import dtype_code
+    m, k = a.shape
+    opt = _cabi.Options(ctypes.sizeof(_cabi.Options), depth, kernel, 0, 0)
+    with torch.cuda.device(a.device):
+        rc = _cabi.lib().b200fp8_gemm_rowcol_f32_allgather(
+            m, k, shard.n, a.data_ptr(), dtype_code(a), b_shard.data_ptr(), dtype_code(b_shard), shared.pointers(),
+            shared.world, shared.rank, n_total, shard.n_begin, ctypes.byref(opt),
+            torch.cuda.current_stream(a.device).cuda_stream)
+    _cabi.check(rc, "gemm_allgather")

@@ -1,0 +1,87 @@
+"""Fused GEMM + all-gather on two or more GPUs of one box (skipped where fewer are visible).
+
+Every rank computes its column block of C and its kernel's epilogue stores the block into every rank's
+full C.  Afterwards each rank's C must equal, bit for bit, the C the same rank computes alone with the
+unsharded operator (same kernels, same K order), and both must satisfy the path's tolerance against the
+FP64 oracle on sampled points.
+"""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, shape, kernel, ret):
+    import numpy as np
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from __graft_entry__ import load_package
+    from oracle import fp8_oracle as fo
+    pkg = load_package()
+    g, sh_mod = pkg.gemm, pkg.shard
+    m, k, n = shape
+    dev = torch.device("cuda", rank)
+    a = torch.empty((m, k), dtype=torch.float8_e4m3fn, device=dev)
+    b = torch.empty((n, k), dtype=torch.float8_e4m3fn, device=dev)
+    g.fill_normal(a, 1.0, 31)                      # replicated operands: same seeds on every rank
+    g.fill_normal(b, 1.0, 32)
+    shared = sh_mod.SharedC(m, n, dev)
+    shared.own.fill_(float("nan"))
+    torch.cuda.synchronize()
+    dist.barrier()
+    sh = sh_mod.column_shard(n, rank, world)
+    for _ in range(2):                             # twice: the second run overwrites a complete matrix
+        sh_mod.gemm_allgather(a, b[sh.n_begin:sh.n_end], shared, sh, n, kernel=kernel)
+        torch.cuda.synchronize()
+        dist.barrier()
+    assert g.device_status() == 0
+    alone = torch.empty((m, n), dtype=torch.float32, device=dev)
+    g.gemm_ex(a, b, alone, kernel=kernel)
+    torch.cuda.synchronize()
+    equal = bool(torch.equal(shared.own, alone))
+    rng = np.random.default_rng(rank)
+    ms, ns = rng.integers(0, m, 512), rng.integers(0, n, 512)
+    C64, S = fo.gemm_f64_points(a.view(torch.uint8).cpu().numpy(), 0, b.view(torch.uint8).cpu().numpy(), 0, ms, ns)
+    got = shared.own[torch.from_numpy(ms).to(dev), torch.from_numpy(ns).to(dev)].cpu().numpy()
+    bad, worst, _ = fo.check_tolerance(got, C64, S)
+    ret[rank] = (equal, int(bad), float(worst))
+    shared.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("shape,kernel", [((1024, 512, 2048), 3), ((2048, 1024, 4096), 5), ((300, 272, 1024), 0)])
+def test_fused_allgather_matches_unsharded(shape, kernel):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_worker, args=(r, world, port, shape, kernel, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        for r in range(world):
+            equal, bad, worst = ret[r]
+            assert equal, f"rank {r}: gathered C differs from the unsharded result"
+            assert bad == 0 and worst <= 1.0
