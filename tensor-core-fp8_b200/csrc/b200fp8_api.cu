@@ -297,10 +297,10 @@ int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, 
     if (n_begin < 0 || n_local < 0 || n_begin + n_local > n_total || (n_begin % 4) || (n_total % 4)) return cudaErrorInvalidValue;
     if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
     PeerSet peers;
-    for (int r = 0; r < world; ++r) {
+    for (int r = 0; r < world; ++r)
         if (!c_all[r] || (reinterpret_cast<uintptr_t>(c_all[r]) % 16)) return cudaErrorInvalidValue;
-        if (r != rank) peers.c[peers.count++] = c_all[r] + n_begin;
-    }
+    // every rank starts with its right-hand neighbour, so that at any moment the ranks store to different GPUs
+    for (int i = 1; i < world; ++i) peers.c[peers.count++] = c_all[(rank + i) % world] + n_begin;
     return gemm_dispatch(m, k, n_local, a, a_dtype, k, b_shard, b_dtype, k, c_all[rank] + n_begin, n_total, options,
                          static_cast<cudaStream_t>(stream), &peers);
 }
