@@ -192,6 +192,7 @@ def main() -> int:
     ap.add_argument("--allgather", action="store_true", help="also time an NCCL all-gather of the C shards (N > 1)")
     ap.add_argument("--fused-allgather", action="store_true",
                     help="also time the GEMM with the all-gather fused into its epilogue (N > 1): every rank ends with all of C")
+    ap.add_argument("--multimem", action="store_true", help="fused all-gather through NVSwitch multicast (multimem stores)")
     ap.add_argument("--kernel", type=int, default=0)
     ap.add_argument("--depth", type=int, default=0)
     ap.add_argument("--a-dtype", default="e4m3", choices=["e4m3", "e5m2"])
@@ -382,7 +383,7 @@ def main() -> int:
 
     # ---- the same step with the all-gather of C fused into the kernel's epilogue (peer stores over NVLink) ----
     if args.fused_allgather and world > 1 and sharded:
-        shared = shard_mod.SharedC(M, N, dev)
+        shared = shard_mod.SharedC(M, N, dev, multicast=args.multimem)
         fsteps = max(3, min(args.steps, 10))
         for _ in range(2):
             shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
@@ -398,7 +399,8 @@ def main() -> int:
         dist.all_reduce(tf, op=dist.ReduceOp.MAX)
         fms = float(tf.item())
         line["fused_allgather"] = {"ms_per_step": fms, "tflops": 2.0 * M * K * N / (fms * 1e-3) / 1e12, "steps": fsteps,
-                                   "nvlink_bytes_sent_per_rank": int(4 * M * n_local * (world - 1)),
+                                   "stores": "multimem (NVSwitch multicast)" if args.multimem else "unicast peer stores",
+                                   "nvlink_bytes_sent_per_rank": int(4 * M * n_local * (1 if args.multimem else world - 1)),
                                    "result": "every rank holds the full row-major C; no separate collective, no re-layout"}
         if g.device_status() != 0:
             raise SystemExit("device status word is non-zero after the fused run")

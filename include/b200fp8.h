@@ -91,10 +91,14 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
  * and no re-layout pass.  Requirements on top of the operator's: n_total and
  * n_begin multiples of 4, every C base 16-byte aligned.  The caller
  * synchronises the ranks (stream sync + barrier) before reading C.
+ * `c_multicast`, when not NULL, is an NVSwitch multicast address bound to the same matrices (all ranks'
+ * C at the same offsets): the epilogue then issues ONE multimem store per 16 bytes, which the switch
+ * delivers to every rank's matrix including the own, instead of one store per peer.
  */
 int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,
-                                      int b_dtype, float* const* c_all, int world, int rank, long long n_total,
-                                      long long n_begin, const b200fp8_options* options, void* stream);
+                                      int b_dtype, float* const* c_all, float* c_multicast, int world, int rank,
+                                      long long n_total, long long n_begin, const b200fp8_options* options,
+                                      void* stream);
 
 /*
  * The whole call sequence of the reference's benchmark driver for one GEMM

@@ -77,7 +77,7 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_gemm_rowcol_f32.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp]
         L.b200fp8_gemm_rowcol_f32_ex.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ll,
                                                  ctypes.POINTER(Options), vp]
-        L.b200fp8_gemm_rowcol_f32_allgather.argtypes = [ci, ci, ci, vp, ci, vp, ci, ctypes.POINTER(vp), ci, ci, ll, ll,
+        L.b200fp8_gemm_rowcol_f32_allgather.argtypes = [ci, ci, ci, vp, ci, vp, ci, ctypes.POINTER(vp), vp, ci, ci, ll, ll,
                                                         ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
         L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]

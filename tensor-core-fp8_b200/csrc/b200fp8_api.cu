@@ -92,6 +92,7 @@ cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes
 struct PeerSet {
     int count = 0;
     float* c[kMaxPeers] = {};
+    float* multicast = nullptr;      // when set, one multimem store replaces the own store and all peer stores
 };
 
 // Tuning knobs read once from the environment (B200FP8_*); defaults are the measured best.
@@ -146,10 +147,14 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
     args.tma_store = ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
     args.C = c; args.ldc = ldc; args.status = ctx.status;
-    if (peers && peers->count > 0) {
+    if (peers && (peers->count > 0 || peers->multicast)) {
         if (!args.tma_store || (n % 4) != 0) return cudaErrorInvalidValue;     // peer stores move whole 16-byte groups
-        args.num_peers = peers->count;
-        for (int i = 0; i < peers->count; ++i) args.peer_c[i] = peers->c[i];
+        if (peers->multicast) {
+            args.mc_c = peers->multicast;
+        } else {
+            args.num_peers = peers->count;
+            for (int i = 0; i < peers->count; ++i) args.peer_c[i] = peers->c[i];
+        }
     }
 
     CUtensorMap ta, tb, tc;
@@ -233,7 +238,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
     if (kernel == B200FP8_KERNEL_SKINNY && m > kSkinnyMaxM) return cudaErrorInvalidValue;
-    if (peers && peers->count > 0 && kernel == B200FP8_KERNEL_SKINNY) kernel = B200FP8_KERNEL_PAIR_N256;
+    if (peers && (peers->count > 0 || peers->multicast) && kernel == B200FP8_KERNEL_SKINNY) kernel = B200FP8_KERNEL_PAIR_N256;
 
 #define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
 #define B200FP8_LAUNCH4(BN, ST, CT, NA) \
@@ -291,8 +296,9 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
 }
 
 int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,
-                                      int b_dtype, float* const* c_all, int world, int rank, long long n_total,
-                                      long long n_begin, const b200fp8_options* options, void* stream) {
+                                      int b_dtype, float* const* c_all, float* c_multicast, int world, int rank,
+                                      long long n_total, long long n_begin, const b200fp8_options* options,
+                                      void* stream) {
     if (world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world || !c_all) return cudaErrorInvalidValue;
     if (n_begin < 0 || n_local < 0 || n_begin + n_local > n_total || (n_begin % 4) || (n_total % 4)) return cudaErrorInvalidValue;
     if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
@@ -301,6 +307,10 @@ int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, 
         if (!c_all[r] || (reinterpret_cast<uintptr_t>(c_all[r]) % 16)) return cudaErrorInvalidValue;
     // every rank starts with its right-hand neighbour, so that at any moment the ranks store to different GPUs
     for (int i = 1; i < world; ++i) peers.c[peers.count++] = c_all[(rank + i) % world] + n_begin;
+    if (c_multicast) {
+        if (reinterpret_cast<uintptr_t>(c_multicast) % 16) return cudaErrorInvalidValue;
+        peers.multicast = c_multicast + n_begin;
+    }
     return gemm_dispatch(m, k, n_local, a, a_dtype, k, b_shard, b_dtype, k, c_all[rank] + n_begin, n_total, options,
                          static_cast<cudaStream_t>(stream), &peers);
 }

@@ -61,6 +61,9 @@ struct GemmArgs {
     // peer_c[p] points at this rank's column block inside peer p's full matrix (row pitch ldc).
     int num_peers;
     float* peer_c[kMaxPeers];
+    // Same, through NVSwitch multicast: one multimem store per 16 bytes reaches every GPU's matrix (own included),
+    // so each box crosses this GPU's NVLink once instead of once per peer.  Replaces the TMA store and peer_c.
+    float* mc_c;
 };
 
 enum : int {
@@ -384,10 +387,11 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (issuer) {
-                        if (row0 < args.M && col0 < args.N && !(args.debug & 2)) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        if (row0 < args.M && col0 < args.N && !(args.debug & 2) && args.mc_c == nullptr)
+                            ptx::tma_store_2d(&tmap_c, sb, col0, row0);
                         ptx::bulk_commit_group();
                     }
-                    if (args.num_peers > 0) {
+                    if (args.num_peers > 0 || args.mc_c != nullptr) {
                         // Read the box back row-contiguously (8 lanes cover one 128-byte row, 4 rows per
                         // instruction) and push it to every peer: full 128-byte lines over NVLink.
                         uint4 w[8];
@@ -398,7 +402,14 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             w[i] = ptx::ld_shared_v4(sb + r * 128 + ((chunk ^ (r & 7)) << 4));
                         }
                         const int col = col0 + chunk * 4;
-                        if (col < args.N) {                        // N % 4 == 0 on this path: whole 16-byte groups
+                        if (col < args.N && args.mc_c != nullptr) {
+                            float* base = args.mc_c + col;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int row = row0 + i * 4 + (lane >> 3);
+                                if (row < args.M) ptx::multimem_st_v4(base + static_cast<long long>(row) * args.ldc, w[i]);
+                            }
+                        } else if (col < args.N) {                 // N % 4 == 0 on this path: whole 16-byte groups
                             for (int p = 0; p < args.num_peers; ++p) {
                                 float* base = args.peer_c[p] + col;
 #pragma unroll

@@ -264,6 +264,14 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
     return v;
 }
 
+// one 16-byte store delivered by NVSwitch to every GPU bound to the multicast address (own GPU included)
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+                   "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 // ---- descriptors ------------------------------------------------------------
 
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes

@@ -63,7 +63,7 @@ class SharedC:
     Call `close()` (collective) when done.
     """
 
-    def __init__(self, m: int, n_total: int, device, group=None):
+    def __init__(self, m: int, n_total: int, device, group=None, multicast: bool = False):
         import ctypes
         import torch
         import torch.distributed as dist
@@ -77,6 +77,23 @@ class SharedC:
             raise ValueError("need at least one column per rank")
         self.device = torch.device(device)
         self._ptrs = [None] * self.world
+        self.multicast_ptr = 0
+        self._symm = None
+        if multicast:
+            # NVSwitch multicast: torch's symmetric memory allocates the matrices, exchanges the handles and
+            # binds them to one multicast address (needs an NCCL-capable process group on this device)
+            import torch.distributed._symmetric_memory as symm_mem
+            with torch.cuda.device(self.device):
+                self.own = symm_mem.empty((m, n_total), dtype=torch.float32, device=self.device)
+                self._symm = symm_mem.rendezvous(self.own, group if group is not None else dist.group.WORLD)
+                if not self._symm.multicast_ptr:
+                    raise RuntimeError("this system offers no NVLink multicast for symmetric memory")
+                self.multicast_ptr = int(self._symm.multicast_ptr)
+                self._ptrs = [int(p) for p in self._symm.buffer_ptrs]
+                self.tensors = [self.own if r == self.rank else self._symm.get_buffer(r, (m, n_total), torch.float32)
+                                for r in range(self.world)]
+                self._check_mappings(torch, dist, group)
+            return
         with torch.cuda.device(self.device):
             own = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)
@@ -92,16 +109,19 @@ class SharedC:
                     self._ptrs[r] = p.value
             self.tensors = [torch.as_tensor(_DevicePointer(p, (m, n_total)), device=self.device) for p in self._ptrs]
             self.own = self.tensors[self.rank]
-            # prove every mapping with copies (a bad mapping fails here with an error, not inside a kernel)
-            mark = torch.full((1,), float(self.rank + 1), dtype=torch.float32, device=self.device)
-            for t in self.tensors:
-                t[0, self.rank:self.rank + 1].copy_(mark)
-            torch.cuda.synchronize(self.device)
-            dist.barrier(group=group)
-            seen = self.own[0, :self.world].cpu().tolist()
-            if seen != [float(r + 1) for r in range(self.world)]:
-                raise RuntimeError(f"peer mapping check failed on rank {self.rank}: {seen}")
-            dist.barrier(group=group)
+            self._check_mappings(torch, dist, group)
+
+    def _check_mappings(self, torch, dist, group):
+        # prove every mapping with copies (a bad mapping fails here with an error, not inside a kernel)
+        mark = torch.full((1,), float(self.rank + 1), dtype=torch.float32, device=self.device)
+        for t in self.tensors:
+            t[0, self.rank:self.rank + 1].copy_(mark)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+        seen = self.own[0, :self.world].cpu().tolist()
+        if seen != [float(r + 1) for r in range(self.world)]:
+            raise RuntimeError(f"peer mapping check failed on rank {self.rank}: {seen}")
+        dist.barrier(group=group)
 
     def pointers(self):
         import ctypes
@@ -115,6 +135,10 @@ class SharedC:
             return
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self._group)
+        if self._symm is not None:                    # torch owns the symmetric allocation and its multicast binding
+            self.tensors, self._ptrs = None, None
+            dist.barrier(group=self._group)
+            return
         self.tensors, self.own = None, None
         with torch.cuda.device(self.device):
             for r, p in enumerate(self._ptrs):
@@ -136,6 +160,6 @@ def gemm_allgather(a, b_shard, shared: "SharedC", shard: Shard, n_total: int, *,
     with torch.cuda.device(a.device):
         rc = _cabi.lib().b200fp8_gemm_rowcol_f32_allgather(
             m, k, shard.n, a.data_ptr(), dtype_code(a), b_shard.data_ptr(), dtype_code(b_shard), shared.pointers(),
-            shared.world, shared.rank, n_total, shard.n_begin, ctypes.byref(opt),
+            shared.multicast_ptr or None, shared.world, shared.rank, n_total, shard.n_begin, ctypes.byref(opt),
             torch.cuda.current_stream(a.device).cuda_stream)
     _cabi.check(rc, "gemm_allgather")

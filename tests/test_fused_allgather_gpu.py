@@ -24,13 +24,16 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, shape, kernel, ret):
+def _worker(rank, world, port, shape, kernel, multicast, ret):
     import numpy as np
     import torch.distributed as dist
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    if multicast:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
     from __graft_entry__ import load_package
     from oracle import fp8_oracle as fo
     pkg = load_package()
@@ -41,7 +44,14 @@ def _worker(rank, world, port, shape, kernel, ret):
     b = torch.empty((n, k), dtype=torch.float8_e4m3fn, device=dev)
     g.fill_normal(a, 1.0, 31)                      # replicated operands: same seeds on every rank
     g.fill_normal(b, 1.0, 32)
-    shared = sh_mod.SharedC(m, n, dev)
+    try:
+        shared = sh_mod.SharedC(m, n, dev, multicast=multicast)
+    except RuntimeError as e:
+        if multicast and "multicast" in str(e):
+            ret[rank] = "no-multicast"
+            dist.destroy_process_group()
+            return
+        raise
     shared.own.fill_(float("nan"))
     torch.cuda.synchronize()
     dist.barrier()
@@ -65,8 +75,9 @@ def _worker(rank, world, port, shape, kernel, ret):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("multicast", [False, True], ids=["peer-stores", "multimem"])
 @pytest.mark.parametrize("shape,kernel", [((1024, 512, 2048), 3), ((2048, 1024, 4096), 5), ((300, 272, 1024), 0)])
-def test_fused_allgather_matches_unsharded(shape, kernel):
+def test_fused_allgather_matches_unsharded(shape, kernel, multicast):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -75,12 +86,14 @@ def test_fused_allgather_matches_unsharded(shape, kernel):
     with ctx.Manager() as mgr:
         ret = mgr.dict()
         port = _free_port()
-        procs = [ctx.Process(target=_worker, args=(r, world, port, shape, kernel, ret)) for r in range(world)]
+        procs = [ctx.Process(target=_worker, args=(r, world, port, shape, kernel, multicast, ret)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
             p.join(300)
             assert p.exitcode == 0
+        if any(ret[r] == "no-multicast" for r in range(world)):
+            pytest.skip("no NVLink multicast support on this system")
         for r in range(world):
             equal, bad, worst = ret[r]
             assert equal, f"rank {r}: gathered C differs from the unsharded result"
