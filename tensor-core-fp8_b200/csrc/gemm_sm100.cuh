@@ -48,7 +48,8 @@ struct GemmArgs {
     int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
     uint32_t wait_hint_ns; // suspend-time hint for long mbarrier waits (0 = plain polling)
     int debug;            // diagnostics only (results become wrong): 1 skip TMA loads, 2 skip C stores, 4 skip MMAs,
-                          // 64 record per-k-block clock64 stamps of CTA 0's MMA warp in `trace`
+                          // 64 record per-k-block clock64 stamps of CTA 0's MMA warp in `trace`,
+                          // 512 leave the third k-block of every CTA's first tile unloaded (exercises the bounded waits)
     float* C;
     long long ldc;
     int* status;          // device status word: 0 = ok, else first error code recorded
@@ -244,7 +245,10 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 const uint32_t a_dst = smem_base + L::kRingOff + s * L::kStageBytes;
                 const uint32_t b_dst = a_dst + L::kABytes;
-                if (ptx::elect_one()) {
+                if ((args.debug & 512) && it == 0 && kb == 2) {
+                    // failure-path test: this ring slot is never armed nor loaded, so the MMA warp's bounded wait on
+                    // it must run out and the kernel must end by itself with a status code
+                } else if (ptx::elect_one()) {
                     if (args.debug & 1) {
                         if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
                     } else if (pair) {
