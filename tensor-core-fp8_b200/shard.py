@@ -163,3 +163,53 @@ def gemm_allgather(a, b_shard, shared: "SharedC", shard: Shard, n_total: int, *,
             shared.multicast_ptr or None, shared.world, shared.rank, n_total, shard.n_begin, ctypes.byref(opt),
             torch.cuda.current_stream(a.device).cuda_stream)
     _cabi.check(rc, "gemm_allgather")
+
+
+class HostShardedGemm:
+    """End to end from HOST buffers on R GPUs: what `b200fp8_gemm_rowcol_f32_host` does on one.
+
+    Uploading the replicated A once per rank would push R copies of it through the host's PCIe complex,
+    so every rank uploads only M/R rows of A (and its own rows of B) and the ranks all-gather A over
+    NVLink (NCCL, in place).  The operator then runs in row blocks whose C rows are downloaded while the
+    next block computes.  `__call__(a_rows_host, b_shard_host, c_shard_host)`: pinned host tensors holding
+    this rank's M/R rows of A, its rows of B and room for its M x n column block of C; returns when the
+    block is complete in host memory.
+    """
+
+    def __init__(self, m: int, k: int, shard: Shard, a_dtype, b_dtype, device, group=None, row_blocks: int = 8):
+        import torch
+        import torch.distributed as dist
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if m % self.world:
+            raise ValueError("M must be divisible by the number of ranks")
+        self.m, self.k, self.shard, self.device = m, k, shard, torch.device(device)
+        self.rows_own = m // self.world
+        self.a = torch.empty((m, k), dtype=a_dtype, device=self.device)
+        self.b = torch.empty((shard.n, k), dtype=b_dtype, device=self.device)
+        self.c = torch.empty((m, shard.n), dtype=torch.float32, device=self.device)
+        step = -(-m // row_blocks)
+        step = -(-step // 256) * 256
+        self.blocks = [(r0, min(m, r0 + step)) for r0 in range(0, m, step)]
+        self.copy_out = torch.cuda.Stream(device=self.device)
+        self.done = [torch.cuda.Event() for _ in self.blocks]
+
+    def __call__(self, a_rows_host, b_shard_host, c_shard_host, *, depth: int = 0, kernel: int = 0):
+        import torch
+        import torch.distributed as dist
+        from . import gemm as g
+        r0 = self.rank * self.rows_own
+        own = self.a[r0:r0 + self.rows_own]
+        own.view(torch.uint8).copy_(a_rows_host.view(torch.uint8), non_blocking=True)
+        self.b.view(torch.uint8).copy_(b_shard_host.view(torch.uint8), non_blocking=True)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.a.view(torch.uint8), own.view(torch.uint8), group=self.group)
+        cur = torch.cuda.current_stream(self.device)
+        for (lo, hi), ev in zip(self.blocks, self.done):
+            g.gemm_ex(self.a[lo:hi], self.b, self.c[lo:hi], depth=depth, kernel=kernel)
+            ev.record(cur)
+            self.copy_out.wait_event(ev)
+            with torch.cuda.stream(self.copy_out):
+                c_shard_host[lo:hi].copy_(self.c[lo:hi], non_blocking=True)
+        self.copy_out.synchronize()
+        cur.synchronize()
