@@ -104,7 +104,9 @@ struct Tune {
     int pace_min_waves = 8;       // tile pacing only pays on long runs
     int pace_limit_ns = 30000;
     int store_gap_ns = 0;
+    int split_tail = 1;
     Tune() {
+        if (const char* v = getenv("B200FP8_SPLIT_TAIL")) split_tail = atoi(v);
         if (const char* v = getenv("B200FP8_STORE_GAP_NS")) store_gap_ns = atoi(v);
         if (const char* v = getenv("B200FP8_PACE_MIN_WAVES")) pace_min_waves = atoi(v);
         if (const char* v = getenv("B200FP8_PACE_LIMIT_NS")) pace_limit_ns = atoi(v);
@@ -168,9 +170,20 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     }
 
     const long long tiles = static_cast<long long>(args.m_tiles) * args.n_tiles;
+    if (tiles > (1LL << 30)) return cudaErrorInvalidValue;
     int units = ctx.sm_count / CTAS;                     // CTAs (or pairs) resident at once
     if (max_ctas > 0 && max_ctas / CTAS < units) units = max_ctas / CTAS > 0 ? max_ctas / CTAS : 1;
     if (tiles < units) units = static_cast<int>(tiles);
+    // tail balancing: a last round that would occupy at most half of the CTAs is run as half-width items
+    const int rem = static_cast<int>(tiles % units);
+    const bool split_tail = NACC == 1 && BN == 256 && tune().split_tail && tiles > units && rem > 0 && 2 * rem <= units;
+    args.split_tiles = split_tail ? rem : 0;
+    args.full_items = static_cast<int>(tiles) - args.split_tiles;
+    args.idesc_half = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN / 2);
+    CUtensorMap tbh = tb;
+    if (split_tail &&
+        (e = encode_2d(&tbh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows / 2)) != cudaSuccess)
+        return e;
 
     // tile pacing for long persistent runs (pairs only): a fresh zeroed counter per launch, stream-ordered
     if (CTAS == 2 && tune().pace_min_waves > 0 && tiles >= static_cast<long long>(tune().pace_min_waves) * units) {
@@ -194,7 +207,7 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, args);
+    e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, tbh, args);
     if (e == cudaSuccess) ++t_launches;
     return e;
 }
@@ -486,6 +499,8 @@ cudaError_t noalloc_launch(const NoAllocDevice& d, int m, int k, int n, const vo
     }
     int units = d.sm_count / 2;
     if (tiles < units) units = static_cast<int>(tiles);
+    args.full_items = static_cast<int>(tiles);
+    args.split_tiles = 0;
     if (tiles >= 8LL * units) {
         // the counter keeps whatever the previous call left: it has to start from zero
         if ((e = cudaMemsetAsync(d.scratch, 0, sizeof(unsigned int), stream)) != cudaSuccess) return e;
@@ -502,7 +517,7 @@ cudaError_t noalloc_launch(const NoAllocDevice& d, int m, int k, int n, const vo
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, gemm_fp8_rowcol_kernel<BN, STAGES, 2, NACC>, ta, tb, tc, args);
+    e = cudaLaunchKernelEx(&cfg, gemm_fp8_rowcol_kernel<BN, STAGES, 2, NACC>, ta, tb, tc, tb, args);
     if (e == cudaSuccess) ++t_launches;
     return e;
 }

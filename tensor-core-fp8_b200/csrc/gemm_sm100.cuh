@@ -45,6 +45,12 @@ struct GemmArgs {
     int n_tiles;          // tiles along N (tile = BN columns)
     int group_m;          // rasterisation: tiles are walked down `group_m` M-tiles before moving along N
     uint32_t idesc;       // UMMA instruction descriptor (dtype pair, tile shape)
+    // Tail balancing (NACC == 1): when the last round of the persistent walk would keep at most half of the
+    // CTAs busy, its `split_tiles` tiles are each processed as two half-width work items (columns [0, BN/2)
+    // and [BN/2, BN)), so that the round takes half a tile time.  Work items with index >= full_items are halves.
+    int full_items;       // number of full-width work items (= tiles - split_tiles)
+    int split_tiles;      // tiles handled as two halves each (0 = off)
+    uint32_t idesc_half;  // instruction descriptor for N = BN / 2
     int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
     uint32_t wait_hint_ns; // suspend-time hint for long mbarrier waits (0 = plain polling)
     int debug;            // diagnostics only (results become wrong): 1 skip TMA loads, 2 skip C stores, 4 skip MMAs,
@@ -143,6 +149,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c,
+                       const __grid_constant__ CUtensorMap tmap_b_half,   // B with boxes of half as many rows (tail items)
                        const GemmArgs args)
 {
     using L = GemmSmem<BN, STAGES, CTAS, NACC>;
@@ -189,22 +196,30 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
-    // persistent tile walk, identical in every role
-    const int num_tiles = args.m_tiles * args.n_tiles;
+    // persistent walk over work items, identical in every role
+    const int num_items = args.full_items + 2 * args.split_tiles;
     const int first_tile = blockIdx.x / CTAS;
     const int tile_step = gridDim.x / CTAS;
     const int nkb = args.num_k_blocks;
 
-    auto tile_coords = [&](int t, int& m0, int& n0) {
+    // work item -> first row / column of this CTA's part; `half` = half-width tail item
+    auto tile_coords = [&](int t, int& m0, int& n0, bool& half) {
+        half = t >= args.full_items;
+        int tile = t, h = 0;
+        if (half) {
+            const int u = t - args.full_items;
+            tile = args.full_items + (u >> 1);
+            h = u & 1;
+        }
         const int per_group = args.group_m * args.n_tiles;
-        const int g = t / per_group;
+        const int g = tile / per_group;
         const int first_m = g * args.group_m;
         const int gsz = min(args.group_m, args.m_tiles - first_m);
-        const int r = t - g * per_group;
+        const int r = tile - g * per_group;
         const int m_blk = first_m + r % gsz;
         const int n_blk = r / gsz;
         m0 = m_blk * (kTileM * CTAS) + static_cast<int>(rank) * kTileM;
-        n0 = n_blk * L::kTileN;
+        n0 = n_blk * L::kTileN + h * (BN / 2);
     };
     // Accumulator slot bookkeeping.  NACC == 1: tile `it` owns slot it & 1 (its (it >> 1)-th use).
     // NACC == 2: every tile owns both slots (slot j holds columns [j*BN, (j+1)*BN); use number = it).
@@ -219,10 +234,13 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int issued = 0;
         bool ok = true;
         int it = 0;
-        for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
+        for (int t = first_tile; t < num_items && ok; t += tile_step, ++it) {
             int m0, n0;
-            tile_coords(t, m0, n0);
-            const int nb0 = n0 + static_cast<int>(rank) * L::kBRows;
+            bool half;
+            tile_coords(t, m0, n0, half);
+            const int nb0 = n0 + static_cast<int>(rank) * (half ? L::kBRows / 2 : L::kBRows);
+            const CUtensorMap* tmb = half ? &tmap_b_half : &tmap_b;
+            const uint32_t tx_bytes = half ? (L::kABytes + L::kBBytes / 2) * CTAS : L::kTxBytes;
             if (args.pace != nullptr && rank == 0 && it > 0) {
                 // Tile pacing: CTAs that share operand panels through L2 only profit while they sweep K
                 // together, and small systematic speed differences between SMs pull them apart over a
@@ -252,17 +270,17 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (args.debug & 1) {
                         if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
                     } else if (pair) {
-                        if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kTxBytes);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
                         ptx::tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, m0, full0 + 8 * s);
 #pragma unroll
                         for (int j = 0; j < NACC; ++j)
-                            ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, &tmap_b, kb * kBlockK, nb0 + j * BN, full0 + 8 * s);
+                            ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kb * kBlockK, nb0 + j * BN, full0 + 8 * s);
                     } else {
-                        ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kTxBytes);
+                        ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
                         ptx::tma_load_2d(a_dst, &tmap_a, kb * kBlockK, m0, bar_full + 8 * s);
 #pragma unroll
                         for (int j = 0; j < NACC; ++j)
-                            ptx::tma_load_2d(b_dst + j * L::kBBytes, &tmap_b, kb * kBlockK, nb0 + j * BN, bar_full + 8 * s);
+                            ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kb * kBlockK, nb0 + j * BN, bar_full + 8 * s);
                     }
                 }
                 __syncwarp();
@@ -272,7 +290,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (args.pace != nullptr && rank == 0) {
             // announce the iterations this pair does not have, so that nobody waits for it
-            const int max_it = (num_tiles + tile_step - 1) / tile_step;
+            const int max_it = (num_items + tile_step - 1) / tile_step;
             if (it < max_it && ptx::elect_one()) atomicAdd(args.pace, static_cast<unsigned int>(max_it - it));
             __syncwarp();
         }
@@ -293,7 +311,8 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t ph = 0;
             int it = 0;
             bool ok = true;
-            for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
+            for (int t = first_tile; t < num_items && ok; t += tile_step, ++it) {
+                const uint32_t idesc = (t >= args.full_items) ? args.idesc_half : args.idesc;
                 // slot 0 of this tile must have been drained; slot 1 (NACC == 2) is awaited just before its first MMA
                 if (!wait_bounded(bar_tempty + 8 * slot_of(it, 0), use_parity(it) ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusMmaTimeout);
@@ -328,7 +347,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         if (ptx::elect_one()) {
 #pragma unroll
                             for (int k = 0; k < kBlockK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
-                                if (!(args.debug & 4)) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, args.idesc, (kb | k) != 0);
+                                if (!(args.debug & 4)) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
                         }
                         __syncwarp();
                     }
@@ -363,12 +382,14 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
         constexpr int kChunks = BN / 32 / (NACC == 1 ? 2 : 1);    // 32-column chunks this warp drains per tile
         int it = 0;
-        for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
+        for (int t = first_tile; t < num_items; t += tile_step, ++it) {
             int m0, n0;
-            tile_coords(t, m0, n0);
+            bool half;
+            tile_coords(t, m0, n0, half);
             const int row0 = m0 + q * 32;
+            const int chunks = half ? kChunks / 2 : kChunks;     // half-width items have half the columns (NACC == 1 only)
             const int slot = slot_of(it, grp);                    // NACC == 1: both groups share the tile's slot
-            const int c_first = (NACC == 1) ? grp * kChunks : 0;
+            const int c_first = (NACC == 1) ? grp * chunks : 0;
             if (!wait_bounded(bar_tfull + 8 * slot, use_parity(it), abort_flag, pair, args.wait_hint_ns)) {
                 record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
                 break;
@@ -448,16 +469,16 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t va[32], vb[32];
             ptx::tmem_ld_32x32(t_addr, va);
 #pragma unroll 1
-            for (int c = 0; c < kChunks; c += 2) {
+            for (int c = 0; c < chunks; c += 2) {
                 ptx::tmem_ld_wait();                              // va = chunk c
-                ptx::tmem_ld_32x32(t_addr + (c + 1) * 32, vb);    // kChunks is even: chunk c+1 exists
+                ptx::tmem_ld_32x32(t_addr + (c + 1) * 32, vb);    // chunks is even: chunk c+1 exists
                 emit(va, c);
                 ptx::tmem_ld_wait();                              // vb = chunk c+1
-                if (c + 2 < kChunks) ptx::tmem_ld_32x32(t_addr + (c + 2) * 32, va);
+                if (c + 2 < chunks) ptx::tmem_ld_32x32(t_addr + (c + 2) * 32, va);
                 else release_slot();
                 if (args.store_gap_ns) __nanosleep(args.store_gap_ns);
                 emit(vb, c + 1);
-                if (args.store_gap_ns && c + 2 < kChunks) __nanosleep(args.store_gap_ns);
+                if (args.store_gap_ns && c + 2 < chunks) __nanosleep(args.store_gap_ns);
             }
         }
         if (issuer) ptx::bulk_wait_group<0>();                    // all stores of this warp are complete

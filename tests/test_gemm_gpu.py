@@ -144,6 +144,23 @@ def test_random_operands_all_kernels(g, oracle, fa, fb, kernel, depth, shape):
     assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), fa, host_bytes(b), fb)
 
 
+@pytest.mark.parametrize("kernel,max_ctas,shape", [
+    (3, 8, (512, 400, 1280)),     # 10 pair tiles on 4 pairs: the last 2 run as 4 half-width items
+    (3, 8, (700, 272, 1200)),     # ragged M and N: 15 tiles, 3 left over, no split (3 > 2) ... and
+    (3, 12, (700, 272, 1200)),    # ... on 6 pairs 3 left over: split into 6 halves, the last one ragged
+    (1, 4, (384, 528, 768)),      # single-CTA kernel: 9 tiles on 4 CTAs, 1 left over
+    (1, 6, (300, 144, 1700)),     # 21 tiles on 6 CTAs, 3 left over, ragged edges
+])
+@pytest.mark.parametrize("fa,fb", [(0, 0), (1, 0)])
+def test_tail_round_split_into_half_width_items(g, oracle, kernel, max_ctas, shape, fa, fb):
+    m, k, n = shape
+    a, b = random_operands(g, m, k, n, fa, fb, seed=91)
+    out = run(g, a, b, m, k, n, kernel=kernel, max_ctas=max_ctas)
+    assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), fa, host_bytes(b), fb)
+    whole = run(g, a, b, m, k, n, kernel=kernel)                 # all tiles at once: no tail, no split
+    assert torch.equal(out, whole)                               # same K order per element either way
+
+
 @pytest.mark.parametrize("m", [1, 2, 7, 16, 17, 31, 32, 33, 64, 65, 127, 128, 129, 255, 257])
 def test_ragged_m(g, oracle, m):
     k, n = 272, 300
