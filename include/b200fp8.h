@@ -76,6 +76,28 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
                                int b_dtype, long long ldb, float* c, long long ldc, const b200fp8_options* options,
                                void* stream);
 
+/* Output types of b200fp8_gemm_rowcol_scaled */
+enum { B200FP8_OUT_F32 = 0, B200FP8_OUT_BF16 = 1, B200FP8_OUT_F16 = 2 };
+
+/*
+ * The operator with the epilogue of the reference's cuBLASLt comparator
+ * (GEMM/src/cublas.cu:37-53, :79-88: alpha, beta, per-tensor scale pointers;
+ * GEMM/src/matmul-fp8-v0.cu:109-111 writes FP16):
+ *
+ *     D = alpha * a_scale * b_scale * (A B^T) + beta * D
+ *
+ * D is M x N with row pitch ldd, FP32, BF16 or FP16 (`d_dtype`), read only when
+ * beta != 0 and updated in place.  `a_scale` / `b_scale` are optional DEVICE
+ * scalars (NULL = 1), read by the kernel, so a producer on the same stream may
+ * still be computing them when this call is enqueued.  Layouts, dtypes and
+ * requirements of A and B as for the plain operator; D must be aligned to its
+ * element size (16 bytes and ldd * element size a multiple of 16 for the fast
+ * store path).  K must be positive.
+ */
+int b200fp8_gemm_rowcol_scaled(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
+                               long long ldb, void* d, int d_dtype, long long ldd, float alpha, float beta,
+                               const float* a_scale, const float* b_scale, const b200fp8_options* options, void* stream);
+
 /*
  * N-sharded multi-GPU GEMM with the all-gather of C fused into the kernel's
  * epilogue (no counterpart in the reference, which is single-GPU; it follows

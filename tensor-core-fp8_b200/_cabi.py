@@ -27,6 +27,7 @@ CMP_LIB_PATH = os.path.join(CSRC, "libb200fp8_cmp.so")
 DECLARED_SYMBOLS = (
     "b200fp8_gemm_rowcol_f32",
     "b200fp8_gemm_rowcol_f32_ex",
+    "b200fp8_gemm_rowcol_scaled",
     "b200fp8_gemm_rowcol_f32_allgather",
     "b200fp8_gemm_rowcol_f32_host",
     "b200fp8_gemm_rowcol_f32_noalloc",
@@ -79,6 +80,8 @@ def lib() -> ctypes.CDLL:
                                                  ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_allgather.argtypes = [ci, ci, ci, vp, ci, vp, ci, ctypes.POINTER(vp), vp, ci, ci, ll, ll,
                                                         ctypes.POINTER(Options), vp]
+        L.b200fp8_gemm_rowcol_scaled.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ci, ll, ctypes.c_float,
+                                                 ctypes.c_float, vp, vp, ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
         L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
         L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]

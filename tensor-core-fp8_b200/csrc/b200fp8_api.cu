@@ -77,13 +77,14 @@ cudaError_t get_ctx(DeviceCtx** out) {
 
 // 2-D tensor map over a row-major matrix of `rows` x `cols` elements with row pitch `ld` elements.
 cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t cols,
-                      uint64_t rows, uint64_t ld, uint32_t box_cols, uint32_t box_rows) {
+                      uint64_t rows, uint64_t ld, uint32_t box_cols, uint32_t box_rows,
+                      CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
@@ -122,7 +123,7 @@ long long* g_trace = nullptr;   // diagnostics buffer (B200FP8_DEBUG & 64)
 template <int BN, int STAGES, int CTAS, int NACC>
 cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
-                        const PeerSet* peers, cudaStream_t stream) {
+                        const PeerSet* peers, const Epilogue* epi, cudaStream_t stream) {
     using L = GemmSmem<BN, STAGES, CTAS, NACC>;
     static bool attr_done[kMaxDevices] = {};
     auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC>;
@@ -147,8 +148,11 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
         args.trace = g_trace;
     }
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
-    args.tma_store = ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
+    const int out_bytes = (epi && epi->out_dtype != 0) ? 2 : 4;
+    args.tma_store = (((ldc * out_bytes) % 16) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
     args.C = c; args.ldc = ldc; args.status = ctx.status;
+    if (epi) args.epi = *epi;
+    if (epi && epi->active && peers && (peers->count > 0 || peers->multicast)) return cudaErrorInvalidValue;
     if (peers && (peers->count > 0 || peers->multicast)) {
         if (!args.tma_store || (n % 4) != 0) return cudaErrorInvalidValue;     // peer stores move whole 16-byte groups
         if (peers->multicast) {
@@ -163,7 +167,10 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     cudaError_t e;
     if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, lda, kBlockK, kTileM)) != cudaSuccess) return e;
     if ((e = encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows)) != cudaSuccess) return e;
-    if (args.tma_store) {
+    if (args.tma_store && out_bytes == 2) {
+        const CUtensorMapDataType t16 = epi->out_dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        if ((e = encode_2d(&tc, t16, 2, c, n, m, ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != cudaSuccess) return e;
+    } else if (args.tma_store) {
         if ((e = encode_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, c, n, m, ldc, 32, 32)) != cudaSuccess) return e;
     } else {
         tc = ta;   // unused by the kernel on this path; any valid descriptor
@@ -216,15 +223,16 @@ bool valid_dtype(int d) { return d == B200FP8_E4M3 || d == B200FP8_E5M2; }
 
 cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
                           long long ldb, float* c, long long ldc, const b200fp8_options* opt, cudaStream_t stream,
-                          const PeerSet* peers = nullptr) {
+                          const PeerSet* peers = nullptr, const Epilogue* epi = nullptr) {
     if (m < 0 || n < 0 || k < 0 || !valid_dtype(a_dtype) || !valid_dtype(b_dtype)) return cudaErrorInvalidValue;
     if (m == 0 || n == 0) return cudaSuccess;
     if (!c || ldc < n) return cudaErrorInvalidValue;
+    if (epi && epi->active && k == 0) return cudaErrorInvalidValue;   // the extended form needs a non-empty K
     if (k == 0) return cudaMemset2DAsync(c, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(n) * 4, m, stream);
     if (!a || !b || lda < k || ldb < k) return cudaErrorInvalidValue;
     if ((k % 16) || (lda % 16) || (ldb % 16)) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(b) % 16) ||
-        (reinterpret_cast<uintptr_t>(c) % 4))
+        (reinterpret_cast<uintptr_t>(c) % ((epi && epi->out_dtype != 0) ? 2 : 4)))
         return cudaErrorInvalidValue;
 
     int depth = opt ? opt->depth : 0;
@@ -255,7 +263,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
 
 #define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
 #define B200FP8_LAUNCH4(BN, ST, CT, NA) \
-    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, stream)
+    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);
@@ -267,7 +275,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
             return depth == 2 ? B200FP8_LAUNCH4(256, 2, 2, 2) : B200FP8_LAUNCH4(256, 4, 2, 2);
         case B200FP8_KERNEL_SKINNY: {
             e = launch_skinny(ctx->sm_count, ctx->status, g_encode, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
-                              depth, split_k, stream);
+                              depth, split_k, epi, stream);
             if (e == cudaSuccess) ++t_launches;
             return e;
         }
@@ -306,6 +314,22 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
                                void* stream) {
     if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
     return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, c, ldc, options, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp8_gemm_rowcol_scaled(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
+                               long long ldb, void* d, int d_dtype, long long ldd, float alpha, float beta,
+                               const float* a_scale, const float* b_scale, const b200fp8_options* options, void* stream) {
+    if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
+    if (d_dtype < B200FP8_OUT_F32 || d_dtype > B200FP8_OUT_F16) return cudaErrorInvalidValue;
+    Epilogue epi{};
+    epi.active = 1;
+    epi.out_dtype = d_dtype;
+    epi.alpha = alpha;
+    epi.beta = beta;
+    epi.a_scale = a_scale;
+    epi.b_scale = b_scale;
+    return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, static_cast<float*>(d), ldd, options,
+                         static_cast<cudaStream_t>(stream), nullptr, &epi);
 }
 
 int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,

@@ -39,7 +39,15 @@ struct SkinnyArgs {
     float* C;
     long long ldc;
     int* status;
+    Epilogue epi;        // extended epilogue (alpha, beta, scales, 16-bit output); inactive for the plain operator
 };
+
+// one element of D under the extended epilogue
+__device__ __forceinline__ void skinny_store_epi(const SkinnyArgs& args, float alpha, long long idx, float acc) {
+    float v = alpha * acc;
+    if (args.epi.beta != 0.0f) v += args.epi.beta * load_out(args.C, idx, args.epi.out_dtype);
+    store_out(args.C, idx, v, args.epi.out_dtype);
+}
 
 template <int MP>
 struct SkinnySmem {
@@ -103,6 +111,12 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
+    float epi_alpha = 1.0f;
+    if (args.epi.active) {
+        epi_alpha = args.epi.alpha;
+        if (args.epi.a_scale) epi_alpha *= *args.epi.a_scale;
+        if (args.epi.b_scale) epi_alpha *= *args.epi.b_scale;
+    }
     const int n_tile = blockIdx.x;
     const int split = blockIdx.y;                  // = rank in the cluster (1 x splits x 1)
     const int n0 = n_tile * kSkinnyTileN;
@@ -189,7 +203,10 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                         const int m = c * 16 + j;
                         if (m < args.M) {
                             if (clustered) park[m * kSkinnyTileN + n_local] = __uint_as_float(v[j]);
-                            else if (n < args.N) args.C[m * args.ldc + n] = __uint_as_float(v[j]);   // 128 contiguous bytes per warp
+                            else if (n < args.N) {
+                                if (args.epi.active) skinny_store_epi(args, epi_alpha, m * args.ldc + n, __uint_as_float(v[j]));
+                                else args.C[m * args.ldc + n] = __uint_as_float(v[j]);   // 128 contiguous bytes per warp
+                            }
                         }
                     }
                 }
@@ -220,7 +237,13 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                     if (s < args.splits) { acc.x += part[s].x; acc.y += part[s].y; acc.z += part[s].z; acc.w += part[s].w; }
                 const int n = n0 + cg * 4;
                 float* dst = args.C + m * args.ldc + n;
-                if (args.vec_store && n + 3 < args.N) {
+                if (args.epi.active) {
+                    const long long idx = m * args.ldc + n;
+                    if (n < args.N) skinny_store_epi(args, epi_alpha, idx, acc.x);
+                    if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, idx + 1, acc.y);
+                    if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, idx + 2, acc.z);
+                    if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, idx + 3, acc.w);
+                } else if (args.vec_store && n + 3 < args.N) {
                     *reinterpret_cast<float4*>(dst) = acc;
                 } else {
                     if (n < args.N) dst[0] = acc.x;
@@ -316,7 +339,7 @@ cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const
 
 inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, int m, int k, int n, const void* a,
                                  long long lda, const void* b, long long ldb, float* c, long long ldc, int a_dtype,
-                                 int b_dtype, int depth, int split_k, cudaStream_t stream) {
+                                 int b_dtype, int depth, int split_k, const Epilogue* epi, cudaStream_t stream) {
     const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
     const int n_tiles = (n + kSkinnyTileN - 1) / kSkinnyTileN;
     if (n_tiles > 65535 * 32) return cudaErrorInvalidValue;
@@ -328,6 +351,7 @@ inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, 
     args.idesc = make_idesc_f8(b_dtype, a_dtype, 128, mp);   // swapped: B feeds the UMMA A operand
     args.C = c; args.ldc = ldc;
     args.status = status;
+    if (epi) args.epi = *epi;
     CUtensorMap tb, ta;
     cudaError_t e;
     if ((e = skinny_encode(enc, &tb, b, k, n, ldb, kSkinnyTileN)) != cudaSuccess) return e;

@@ -32,9 +32,40 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "ptx_sm100.cuh"
 
 namespace b200fp8 {
+
+// Extended epilogue: D = alpha * sa * sb * (A B^T) + beta * D, D in FP32, BF16 or FP16.
+// The plain operator (alpha = 1, beta = 0, FP32) leaves `active` at 0 and pays nothing for it.
+struct Epilogue {
+    int active;            // 0: plain FP32 store of the accumulator
+    int out_dtype;         // 0 FP32, 1 BF16, 2 FP16
+    float alpha, beta;
+    const float* a_scale;  // optional device scalars multiplied into alpha
+    const float* b_scale;
+};
+
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, int out_dtype) {
+    if (out_dtype == 1) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&p);
+    }
+    const __half2 p = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+__device__ __forceinline__ float load_out(const void* base, long long idx, int out_dtype) {
+    if (out_dtype == 0) return static_cast<const float*>(base)[idx];
+    if (out_dtype == 1) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
+    return __half2float(static_cast<const __half*>(base)[idx]);
+}
+__device__ __forceinline__ void store_out(void* base, long long idx, float v, int out_dtype) {
+    if (out_dtype == 0) static_cast<float*>(base)[idx] = v;
+    else if (out_dtype == 1) static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+    else static_cast<__half*>(base)[idx] = __float2half_rn(v);
+}
 
 constexpr int kMaxPeers = 7;         // one box of 8 GPUs
 
@@ -66,6 +97,7 @@ struct GemmArgs {
     // Fused all-gather of C (N-sharded multi-GPU run): every finished box is also stored, with plain
     // 16-byte stores over NVLink, into the same position of the C matrix of each peer GPU.
     // peer_c[p] points at this rank's column block inside peer p's full matrix (row pitch ldc).
+    Epilogue epi;
     int num_peers;
     float* peer_c[kMaxPeers];
     // Same, through NVSwitch multicast: one multimem store per 16 bytes reaches every GPU's matrix (own included),
@@ -381,6 +413,12 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t tempty0 = pair ? ptx::mapa(bar_tempty, 0) : bar_tempty;
         const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
         constexpr int kChunks = BN / 32 / (NACC == 1 ? 2 : 1);    // 32-column chunks this warp drains per tile
+        float epi_alpha = 1.0f;
+        if (args.epi.active) {
+            epi_alpha = args.epi.alpha;
+            if (args.epi.a_scale) epi_alpha *= *args.epi.a_scale;
+            if (args.epi.b_scale) epi_alpha *= *args.epi.b_scale;
+        }
         int it = 0;
         for (int t = first_tile; t < num_items; t += tile_step, ++it) {
             int m0, n0;
@@ -399,10 +437,44 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN + c_first * 32;
             const int col_base = n0 + (NACC == 2 ? grp * BN : 0) + c_first * 32;
 
+            // extended epilogue: scale the chunk in registers (and add beta * old D, read row by row)
+            auto scale = [&](uint32_t (&v)[32], int c) {
+                if (!args.epi.active) return;
+                const int col0 = col_base + c * 32;
+                const int row = row0 + lane;
+                if (args.epi.beta != 0.0f && row < args.M) {
+                    const long long base = static_cast<long long>(row) * args.ldc + col0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float old = (col0 + i < args.N) ? load_out(args.C, base + i, args.epi.out_dtype) : 0.0f;
+                        v[i] = __float_as_uint(epi_alpha * __uint_as_float(v[i]) + args.epi.beta * old);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(epi_alpha * __uint_as_float(v[i]));
+                }
+            };
             // one chunk: registers -> swizzled staging box -> TMA store (or plain stores when C is not TMA-able)
             auto emit = [&](const uint32_t (&v)[32], int c) {
                 const int col0 = col_base + c * 32;
-                if (args.tma_store) {
+                if (args.tma_store && args.epi.out_dtype != 0) {
+                    // 16-bit output: the box is 32 rows x 64 bytes, unswizzled
+                    if (issuer) ptx::bulk_wait_group_read<0>();
+                    __syncwarp();
+                    const uint32_t row_addr = sb + lane * 64;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        ptx::st_shared_v4(row_addr + i * 16, pack16(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1]), args.epi.out_dtype),
+                                          pack16(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]), args.epi.out_dtype),
+                                          pack16(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]), args.epi.out_dtype),
+                                          pack16(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]), args.epi.out_dtype));
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (issuer) {
+                        if (row0 < args.M && col0 < args.N) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        ptx::bulk_commit_group();
+                    }
+                } else if (args.tma_store) {
                     if (issuer) ptx::bulk_wait_group_read<0>();   // the previous store has finished reading the box
                     __syncwarp();
                     const uint32_t row_addr = sb + lane * 128;
@@ -449,10 +521,10 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 } else {
                     const int row = row0 + lane;
                     if (row < args.M) {
-                        float* dst = args.C + static_cast<long long>(row) * args.ldc + col0;
+                        const long long base = static_cast<long long>(row) * args.ldc + col0;
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (col0 + i < args.N) dst[i] = __uint_as_float(v[i]);
+                            if (col0 + i < args.N) store_out(args.C, base + i, __uint_as_float(v[i]), args.epi.out_dtype);
                     }
                 }
             };
@@ -472,8 +544,10 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int c = 0; c < chunks; c += 2) {
                 ptx::tmem_ld_wait();                              // va = chunk c
                 ptx::tmem_ld_32x32(t_addr + (c + 1) * 32, vb);    // chunks is even: chunk c+1 exists
+                scale(va, c);
                 emit(va, c);
                 ptx::tmem_ld_wait();                              // vb = chunk c+1
+                scale(vb, c + 1);
                 if (c + 2 < chunks) ptx::tmem_ld_32x32(t_addr + (c + 2) * 32, va);
                 else release_slot();
                 if (args.store_gap_ns) __nanosleep(args.store_gap_ns);

@@ -73,6 +73,37 @@ def gemm_ex(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
                  b.stride(0) if n > 1 else k, ldc if ldc is not None else (out.stride(0) if m > 1 else n))
 
 
+OUT_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def gemm_scaled(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: float = 1.0, beta: float = 0.0,
+                a_scale: torch.Tensor | None = None, b_scale: torch.Tensor | None = None, depth: int = 0,
+                kernel: int = KERNEL_AUTO, split_k: int = 0, max_ctas: int = 0):
+    """D = alpha * a_scale * b_scale * (A B^T) + beta * D, D float32 / bfloat16 / float16 (updated in place).
+
+    The epilogue of the reference's cuBLASLt comparator (GEMM/src/cublas.cu:37-53): alpha, beta and
+    per-tensor scale pointers (one-element float32 CUDA tensors here, or None).
+    """
+    m, k = a.shape
+    n, k2 = b.shape
+    if k != k2 or d.shape != (m, n):
+        raise ValueError("shape mismatch")
+    if d.dtype not in OUT_DTYPES:
+        raise TypeError("d must be float32, bfloat16 or float16")
+    for s_ in (a_scale, b_scale):
+        if s_ is not None and (s_.dtype != torch.float32 or not s_.is_cuda or s_.numel() != 1):
+            raise TypeError("scales are one-element float32 CUDA tensors")
+    opt = Options(ctypes.sizeof(Options), depth, kernel, split_k, max_ctas)
+    with torch.cuda.device(d.device):
+        rc = _cabi.lib().b200fp8_gemm_rowcol_scaled(
+            m, k, n, a.data_ptr(), dtype_code(a), a.stride(0) if m > 1 else k, b.data_ptr(), dtype_code(b),
+            b.stride(0) if n > 1 else k, d.data_ptr(), OUT_DTYPES[d.dtype], d.stride(0) if m > 1 else n,
+            float(alpha), float(beta), a_scale.data_ptr() if a_scale is not None else None,
+            b_scale.data_ptr() if b_scale is not None else None, ctypes.byref(opt), _stream_ptr(d.device))
+    _cabi.check(rc, "gemm_scaled")
+    return d
+
+
 def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, depth: int = 0):
     """BmFN's whole sequence with HOST tensors (GEMM/gemm_main.cpp:56-64, :77, :161): upload, run, download."""
     if a.is_cuda or b.is_cuda or out.is_cuda:

@@ -200,6 +200,50 @@ def test_zero_k_and_empty(g):
     del a, b
 
 
+# ---------------------------------------------------------------- extended epilogue (alpha, beta, scales, 16-bit outputs)
+
+@pytest.mark.parametrize("out_dtype,eps", [(torch.float32, 2.0 ** -22), (torch.bfloat16, 2.0 ** -8), (torch.float16, 2.0 ** -11)])
+@pytest.mark.parametrize("kernel,shape,pitch_pad", [(2, (256, 272, 384), 0), (3, (300, 528, 520), 0), (5, (512, 400, 1030), 2),
+                                                    (4, (24, 1024, 520), 0), (4, (100, 2048, 384), 0), (1, (130, 144, 259), 1),
+                                                    (3, (512, 256, 512), 8)])
+@pytest.mark.parametrize("beta", [0.0, 0.75])
+def test_scaled_epilogue(g, oracle, out_dtype, eps, kernel, shape, pitch_pad, beta):
+    """D = alpha*sa*sb*(A B^T) + beta*D against the FP64 oracle.  Tolerance: the path's rule scaled by
+    |alpha*sa*sb|, plus the output format's rounding (eps * |expected|), plus the rounding of the old D term."""
+    m, k, n = shape
+    a, b = random_operands(g, m, k, n, 0, 1, seed=5 + kernel)
+    alpha, sa, sb = 0.5, 0.25, 3.0
+    sa_t = torch.tensor([sa], dtype=torch.float32, device="cuda")
+    sb_t = torch.tensor([sb], dtype=torch.float32, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    buf = torch.randn((m, n + pitch_pad), generator=gen, device="cuda").to(out_dtype)
+    old = buf[:, :n].float().cpu().numpy().astype(np.float64)
+    d = buf[:, :n]                                      # row pitch n + pitch_pad: exercises the non-TMA store path too
+    pad_before = buf[:, n:].clone()
+    g.gemm_scaled(a, b, d, alpha=alpha, beta=beta, a_scale=sa_t, b_scale=sb_t, kernel=kernel)
+    torch.cuda.synchronize()
+    assert g.device_status() == 0
+    C64, S = oracle.gemm_f64(host_bytes(a), 0, host_bytes(b), 1)
+    f = alpha * sa * sb
+    want = f * C64 + beta * old
+    tol = abs(f) * (1e-3 * S + 1e-6) + eps * np.abs(want) + 1e-6 * np.abs(beta * old)
+    got = d.float().cpu().numpy().astype(np.float64)
+    worst = np.max(np.abs(got - want) / tol)
+    assert worst <= 1.0, worst
+    if pitch_pad:                                       # the padding columns are untouched
+        assert torch.equal(buf[:, n:], pad_before)
+
+
+def test_scaled_epilogue_with_unit_factors_equals_plain_operator(g):
+    m, k, n = 512, 384, 768
+    a, b = random_operands(g, m, k, n, 0, 0, seed=2)
+    plain = run(g, a, b, m, k, n, kernel=3)
+    d = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    g.gemm_scaled(a, b, d, kernel=3)
+    torch.cuda.synchronize()
+    assert torch.equal(d, plain)
+
+
 # ---------------------------------------------------------------- memory safety: canaries instead of a sanitizer
 
 @pytest.mark.parametrize("kernel,m,n,ldc", [(2, 130, 132, 160), (3, 300, 260, 264), (1, 129, 257, 257), (4, 20, 130, 131),
