@@ -25,6 +25,12 @@
 // wins on large problems, where the GPU runs at its power limit and energy per flop
 // decides the clock.
 //
+// Also in this kernel: tail balancing (a last round that would keep at most half of the CTAs busy
+// runs as half-width work items), tile pacing (leaders briefly wait for each other before a new
+// tile so that panels are shared through L2), the scaled epilogue (alpha, beta, scale pointers,
+// BF16/FP16 output) and, for N-sharded multi-GPU runs, the fused all-gather (finished boxes are
+// also stored into every peer's C, by unicast stores or one multimem store).
+//
 // Every wait on an mbarrier is bounded: after about two seconds the waiting warp records a
 // code in the device status word, raises a CTA-wide abort flag and leaves its loop, so a
 // broken pipeline ends the kernel instead of hanging the GPU.
