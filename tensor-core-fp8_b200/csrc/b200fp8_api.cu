@@ -149,7 +149,10 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     }
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
     const int out_bytes = (epi && epi->out_dtype != 0) ? 2 : 4;
-    args.tma_store = (((ldc * out_bytes) % 16) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
+    // TMA stores clip at 16-byte granularity: a row end that is not a multiple of 16 bytes would spill into the
+    // pitch padding, so such shapes take the plain-store epilogue
+    args.tma_store = (((ldc * out_bytes) % 16) == 0 && ((static_cast<long long>(n) * out_bytes) % 16) == 0 &&
+                      (reinterpret_cast<uintptr_t>(c) % 16) == 0) ? 1 : 0;
     args.C = c; args.ldc = ldc; args.status = ctx.status;
     if (epi) args.epi = *epi;
     if (epi && epi->active && peers && (peers->count > 0 || peers->multicast)) return cudaErrorInvalidValue;

@@ -247,6 +247,7 @@ def test_scaled_epilogue_with_unit_factors_equals_plain_operator(g):
 # ---------------------------------------------------------------- memory safety: canaries instead of a sanitizer
 
 @pytest.mark.parametrize("kernel,m,n,ldc", [(2, 130, 132, 160), (3, 300, 260, 264), (1, 129, 257, 257), (4, 20, 130, 131),
+                                            (3, 300, 1030, 1032), (5, 512, 1029, 1032), (1, 130, 259, 260), (2, 130, 130, 132),
                                             (5, 300, 772, 776), (5, 257, 515, 515),
                                             (4, 100, 260, 272)])
 def test_no_write_outside_c(g, oracle, kernel, m, n, ldc):
