@@ -76,8 +76,8 @@ int b200fp8_gemm_rowcol_f32_ex(int m, int k, int n, const void* a, int a_dtype, 
                                int b_dtype, long long ldb, float* c, long long ldc, const b200fp8_options* options,
                                void* stream);
 
-/* Output types of b200fp8_gemm_rowcol_scaled */
-enum { B200FP8_OUT_F32 = 0, B200FP8_OUT_BF16 = 1, B200FP8_OUT_F16 = 2 };
+/* Output types of b200fp8_gemm_rowcol_scaled (the first three) and b200fp8_gemm_rowcol_epilogue (all) */
+enum { B200FP8_OUT_F32 = 0, B200FP8_OUT_BF16 = 1, B200FP8_OUT_F16 = 2, B200FP8_OUT_E4M3 = 3, B200FP8_OUT_E5M2 = 4 };
 
 /*
  * The operator with the epilogue of the reference's cuBLASLt comparator
@@ -97,6 +97,39 @@ enum { B200FP8_OUT_F32 = 0, B200FP8_OUT_BF16 = 1, B200FP8_OUT_F16 = 2 };
 int b200fp8_gemm_rowcol_scaled(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
                                long long ldb, void* d, int d_dtype, long long ldd, float alpha, float beta,
                                const float* a_scale, const float* b_scale, const b200fp8_options* options, void* stream);
+
+/*
+ * Full epilogue of the reference's cuBLASLt comparator: what the call above does,
+ * plus the output scale, the absolute maximum and a bias vector, and 8-bit output
+ * (GEMM/src/cublas.cu:37-53 sets A/B/D scale pointers on the matmul descriptor;
+ * GEMM/include/helper.h:59-66 carries the amax and scale slots):
+ *
+ *     t      = alpha * a_scale * b_scale * (A B^T) + beta * D + bias[n]
+ *     amax_d = max over the M x N result of |t|          (NaNs are ignored)
+ *     D      = convert(d_scale * t)
+ *
+ * d_dtype: any B200FP8_OUT_*.  8-bit outputs round to nearest even and saturate to
+ * the largest finite value (448 for E4M3, 57344 for E5M2), as the toolkit's host
+ * conversions do.  With beta != 0 the old D is read in d_dtype.  All pointers in
+ * the struct are DEVICE pointers and optional (NULL = scale 1 / no amax / no bias).
+ * amax_d is zeroed on `stream` before the kernel and written by atomic max, so it
+ * is complete when the kernel has finished.  bias holds N values of bias_dtype
+ * (B200FP8_OUT_F32, _BF16 or _F16).  K must be positive.
+ */
+typedef struct b200fp8_epilogue {
+    int struct_bytes;      /* sizeof(b200fp8_epilogue) */
+    float alpha, beta;
+    const float* a_scale;
+    const float* b_scale;
+    const float* d_scale;
+    float* amax_d;
+    const void* bias;
+    int bias_dtype;
+} b200fp8_epilogue;
+
+int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b,
+                                 int b_dtype, long long ldb, void* d, int d_dtype, long long ldd,
+                                 const b200fp8_epilogue* epilogue, const b200fp8_options* options, void* stream);
 
 /*
  * N-sharded multi-GPU GEMM with the all-gather of C fused into the kernel's

@@ -28,6 +28,7 @@ DECLARED_SYMBOLS = (
     "b200fp8_gemm_rowcol_f32",
     "b200fp8_gemm_rowcol_f32_ex",
     "b200fp8_gemm_rowcol_scaled",
+    "b200fp8_gemm_rowcol_epilogue",
     "b200fp8_gemm_rowcol_f32_allgather",
     "b200fp8_gemm_rowcol_f32_host",
     "b200fp8_gemm_rowcol_f32_noalloc",
@@ -52,6 +53,13 @@ OPERATOR_SYMBOLS = tuple(
 class Options(ctypes.Structure):
     _fields_ = [("struct_bytes", ctypes.c_int), ("depth", ctypes.c_int), ("kernel", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("max_ctas", ctypes.c_int)]
+
+
+class EpilogueDesc(ctypes.Structure):
+    """b200fp8_epilogue of include/b200fp8.h."""
+    _fields_ = [("struct_bytes", ctypes.c_int), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
+                ("a_scale", ctypes.c_void_p), ("b_scale", ctypes.c_void_p), ("d_scale", ctypes.c_void_p),
+                ("amax_d", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("bias_dtype", ctypes.c_int)]
 
 
 class B200Fp8Error(RuntimeError):
@@ -82,6 +90,8 @@ def lib() -> ctypes.CDLL:
                                                         ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_scaled.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ci, ll, ctypes.c_float,
                                                  ctypes.c_float, vp, vp, ctypes.POINTER(Options), vp]
+        L.b200fp8_gemm_rowcol_epilogue.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ci, ll,
+                                                   ctypes.POINTER(EpilogueDesc), ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
         L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
         L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]

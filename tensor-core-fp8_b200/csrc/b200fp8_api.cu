@@ -148,7 +148,7 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
         args.trace = g_trace;
     }
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
-    const int out_bytes = (epi && epi->out_dtype != 0) ? 2 : 4;
+    const int out_bytes = epi ? out_dtype_bytes(epi->out_dtype) : 4;
     // TMA stores clip at 16-byte granularity: a row end that is not a multiple of 16 bytes would spill into the
     // pitch padding, so such shapes take the plain-store epilogue
     args.tma_store = (((ldc * out_bytes) % 16) == 0 && ((static_cast<long long>(n) * out_bytes) % 16) == 0 &&
@@ -170,7 +170,9 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     cudaError_t e;
     if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, lda, kBlockK, kTileM)) != cudaSuccess) return e;
     if ((e = encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows)) != cudaSuccess) return e;
-    if (args.tma_store && out_bytes == 2) {
+    if (args.tma_store && out_bytes == 1) {
+        if ((e = encode_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, c, n, m, ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != cudaSuccess) return e;
+    } else if (args.tma_store && out_bytes == 2) {
         const CUtensorMapDataType t16 = epi->out_dtype == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
         if ((e = encode_2d(&tc, t16, 2, c, n, m, ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != cudaSuccess) return e;
     } else if (args.tma_store) {
@@ -235,7 +237,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     if (!a || !b || lda < k || ldb < k) return cudaErrorInvalidValue;
     if ((k % 16) || (lda % 16) || (ldb % 16)) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(b) % 16) ||
-        (reinterpret_cast<uintptr_t>(c) % ((epi && epi->out_dtype != 0) ? 2 : 4)))
+        (reinterpret_cast<uintptr_t>(c) % (epi ? out_dtype_bytes(epi->out_dtype) : 4)))
         return cudaErrorInvalidValue;
 
     int depth = opt ? opt->depth : 0;
@@ -333,6 +335,34 @@ int b200fp8_gemm_rowcol_scaled(int m, int k, int n, const void* a, int a_dtype, 
     epi.b_scale = b_scale;
     return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, static_cast<float*>(d), ldd, options,
                          static_cast<cudaStream_t>(stream), nullptr, &epi);
+}
+
+int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b,
+                                 int b_dtype, long long ldb, void* d, int d_dtype, long long ldd,
+                                 const b200fp8_epilogue* ep, const b200fp8_options* options, void* stream) {
+    if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
+    if (!ep || ep->struct_bytes != static_cast<int>(sizeof(b200fp8_epilogue))) return cudaErrorInvalidValue;
+    if (d_dtype < B200FP8_OUT_F32 || d_dtype > B200FP8_OUT_E5M2) return cudaErrorInvalidValue;
+    if (ep->bias && (ep->bias_dtype < B200FP8_OUT_F32 || ep->bias_dtype > B200FP8_OUT_F16)) return cudaErrorInvalidValue;
+    if (ep->bias && (reinterpret_cast<uintptr_t>(ep->bias) % out_dtype_bytes(ep->bias_dtype))) return cudaErrorInvalidValue;
+    if ((ep->amax_d && (reinterpret_cast<uintptr_t>(ep->amax_d) % 4)) || m < 0 || n < 0 || k <= 0) return cudaErrorInvalidValue;
+    Epilogue epi{};
+    epi.active = 1;
+    epi.out_dtype = d_dtype;
+    epi.alpha = ep->alpha;
+    epi.beta = ep->beta;
+    epi.a_scale = ep->a_scale;
+    epi.b_scale = ep->b_scale;
+    epi.d_scale = ep->d_scale;
+    epi.amax = ep->amax_d;
+    epi.bias = ep->bias;
+    epi.bias_dtype = ep->bias_dtype;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (ep->amax_d) {                            // the kernel merges by atomic max: start from zero, stream-ordered
+        cudaError_t e = cudaMemsetAsync(ep->amax_d, 0, sizeof(float), st);
+        if (e != cudaSuccess) return e;
+    }
+    return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, static_cast<float*>(d), ldd, options, st, nullptr, &epi);
 }
 
 int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,

@@ -42,11 +42,14 @@ struct SkinnyArgs {
     Epilogue epi;        // extended epilogue (alpha, beta, scales, 16-bit output); inactive for the plain operator
 };
 
-// one element of D under the extended epilogue
-__device__ __forceinline__ void skinny_store_epi(const SkinnyArgs& args, float alpha, long long idx, float acc) {
+// one element of D (column n) under the extended epilogue; `amax` is the thread's running |t| maximum
+__device__ __forceinline__ void skinny_store_epi(const SkinnyArgs& args, float alpha, float dscale, long long idx, int n,
+                                                 float acc, float& amax) {
     float v = alpha * acc;
     if (args.epi.beta != 0.0f) v += args.epi.beta * load_out(args.C, idx, args.epi.out_dtype);
-    store_out(args.C, idx, v, args.epi.out_dtype);
+    if (args.epi.bias != nullptr) v += load_out(args.epi.bias, n, args.epi.bias_dtype);
+    amax = fmaxf(amax, fabsf(v));
+    store_out(args.C, idx, dscale * v, args.epi.out_dtype);
 }
 
 template <int MP>
@@ -111,11 +114,12 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
 
-    float epi_alpha = 1.0f;
+    float epi_alpha = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
     if (args.epi.active) {
         epi_alpha = args.epi.alpha;
         if (args.epi.a_scale) epi_alpha *= *args.epi.a_scale;
         if (args.epi.b_scale) epi_alpha *= *args.epi.b_scale;
+        if (args.epi.d_scale) epi_dscale = *args.epi.d_scale;
     }
     const int n_tile = blockIdx.x;
     const int split = blockIdx.y;                  // = rank in the cluster (1 x splits x 1)
@@ -204,7 +208,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                         if (m < args.M) {
                             if (clustered) park[m * kSkinnyTileN + n_local] = __uint_as_float(v[j]);
                             else if (n < args.N) {
-                                if (args.epi.active) skinny_store_epi(args, epi_alpha, m * args.ldc + n, __uint_as_float(v[j]));
+                                if (args.epi.active) skinny_store_epi(args, epi_alpha, epi_dscale, m * args.ldc + n, n, __uint_as_float(v[j]), epi_amax);
                                 else args.C[m * args.ldc + n] = __uint_as_float(v[j]);   // 128 contiguous bytes per warp
                             }
                         }
@@ -239,10 +243,10 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                 float* dst = args.C + m * args.ldc + n;
                 if (args.epi.active) {
                     const long long idx = m * args.ldc + n;
-                    if (n < args.N) skinny_store_epi(args, epi_alpha, idx, acc.x);
-                    if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, idx + 1, acc.y);
-                    if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, idx + 2, acc.z);
-                    if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, idx + 3, acc.w);
+                    if (n < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx, n, acc.x, epi_amax);
+                    if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 1, n + 1, acc.y, epi_amax);
+                    if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 2, n + 2, acc.z, epi_amax);
+                    if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 3, n + 3, acc.w, epi_amax);
                 } else if (args.vec_store && n + 3 < args.N) {
                     *reinterpret_cast<float4*>(dst) = acc;
                 } else {
@@ -257,6 +261,8 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }
+    __syncwarp();
+    if (args.epi.amax != nullptr) amax_merge_warp(args.epi.amax, epi_amax);
 
     ptx::tc_fence_before();
     __syncthreads();

@@ -40,20 +40,33 @@
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include "ptx_sm100.cuh"
 
 namespace b200fp8 {
 
-// Extended epilogue: D = alpha * sa * sb * (A B^T) + beta * D, D in FP32, BF16 or FP16.
-// The plain operator (alpha = 1, beta = 0, FP32) leaves `active` at 0 and pays nothing for it.
+// Extended epilogue:
+//     t = alpha * sa * sb * (A B^T) + beta * D + bias[n]        amax = max |t| over the valid part of D
+//     D = convert(sd * t)                                       D in FP32, BF16, FP16, E4M3 or E5M2
+// (the knobs of the reference's cuBLASLt comparator, GEMM/src/cublas.cu:37-53: alpha, beta, scale pointers;
+// 8-bit outputs are rounded to nearest even and saturate to the largest finite value, like the toolkit's
+// host conversions that the reference uses for its inputs).  The plain operator (alpha = 1, beta = 0, FP32)
+// leaves `active` at 0 and pays nothing for it.
 struct Epilogue {
     int active;            // 0: plain FP32 store of the accumulator
-    int out_dtype;         // 0 FP32, 1 BF16, 2 FP16
+    int out_dtype;         // 0 FP32, 1 BF16, 2 FP16, 3 E4M3, 4 E5M2
     float alpha, beta;
     const float* a_scale;  // optional device scalars multiplied into alpha
     const float* b_scale;
+    const float* d_scale;  // optional device scalar applied just before the conversion to out_dtype
+    float* amax;           // optional device float (zero at launch): receives max |t| by atomic max; NaNs are ignored
+    const void* bias;      // optional device vector of N values added to every row
+    int bias_dtype;        // 0 FP32, 1 BF16, 2 FP16
 };
 
+__host__ __device__ __forceinline__ int out_dtype_bytes(int out_dtype) {
+    return out_dtype == 0 ? 4 : out_dtype <= 2 ? 2 : 1;
+}
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, int out_dtype) {
     if (out_dtype == 1) {
         const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
@@ -62,15 +75,33 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int out_dtype) {
     const __half2 p = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&p);
 }
+// four floats -> four 8-bit floats (byte 0 = f0), round to nearest even, saturate to finite
+__device__ __forceinline__ uint32_t pack8(float f0, float f1, float f2, float f3, int out_dtype) {
+    const __nv_fp8_interpretation_t fmt = out_dtype == 3 ? __NV_E4M3 : __NV_E5M2;
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, fmt);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f2, f3), __NV_SATFINITE, fmt);
+    return lo | (hi << 16);
+}
 __device__ __forceinline__ float load_out(const void* base, long long idx, int out_dtype) {
     if (out_dtype == 0) return static_cast<const float*>(base)[idx];
     if (out_dtype == 1) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[idx]);
-    return __half2float(static_cast<const __half*>(base)[idx]);
+    if (out_dtype == 2) return __half2float(static_cast<const __half*>(base)[idx]);
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<const __nv_fp8_storage_t*>(base)[idx],
+                                                 out_dtype == 3 ? __NV_E4M3 : __NV_E5M2);
+    return __half2float(__half(h));
 }
 __device__ __forceinline__ void store_out(void* base, long long idx, float v, int out_dtype) {
     if (out_dtype == 0) static_cast<float*>(base)[idx] = v;
     else if (out_dtype == 1) static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
-    else static_cast<__half*>(base)[idx] = __float2half_rn(v);
+    else if (out_dtype == 2) static_cast<__half*>(base)[idx] = __float2half_rn(v);
+    else static_cast<__nv_fp8_storage_t*>(base)[idx] =
+             __nv_cvt_float_to_fp8(v, __NV_SATFINITE, out_dtype == 3 ? __NV_E4M3 : __NV_E5M2);
+}
+// merges a thread's running maximum into the device word (non-negative floats order like their bit patterns)
+__device__ __forceinline__ void amax_merge_warp(float* amax, float local) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, o));
+    if ((threadIdx.x & 31) == 0 && local > 0.0f) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(local));
 }
 
 constexpr int kMaxPeers = 7;         // one box of 8 GPUs
@@ -419,11 +450,12 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t tempty0 = pair ? ptx::mapa(bar_tempty, 0) : bar_tempty;
         const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
         constexpr int kChunks = BN / 32 / (NACC == 1 ? 2 : 1);    // 32-column chunks this warp drains per tile
-        float epi_alpha = 1.0f;
+        float epi_alpha = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
         if (args.epi.active) {
             epi_alpha = args.epi.alpha;
             if (args.epi.a_scale) epi_alpha *= *args.epi.a_scale;
             if (args.epi.b_scale) epi_alpha *= *args.epi.b_scale;
+            if (args.epi.d_scale) epi_dscale = *args.epi.d_scale;
         }
         int it = 0;
         for (int t = first_tile; t < num_items; t += tile_step, ++it) {
@@ -443,7 +475,8 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN + c_first * 32;
             const int col_base = n0 + (NACC == 2 ? grp * BN : 0) + c_first * 32;
 
-            // extended epilogue: scale the chunk in registers (and add beta * old D, read row by row)
+            // extended epilogue, in registers: t = alpha' * acc + beta * old D + bias (old D read row by row),
+            // running |t| maximum over the valid part, then the output scale
             auto scale = [&](uint32_t (&v)[32], int c) {
                 if (!args.epi.active) return;
                 const int col0 = col_base + c * 32;
@@ -459,11 +492,47 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(epi_alpha * __uint_as_float(v[i]));
                 }
+                if (args.epi.bias != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < args.N)
+                            v[i] = __float_as_uint(__uint_as_float(v[i]) + load_out(args.epi.bias, col0 + i, args.epi.bias_dtype));
+                }
+                if (args.epi.amax != nullptr && row < args.M) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < args.N) epi_amax = fmaxf(epi_amax, fabsf(__uint_as_float(v[i])));
+                }
+                if (args.epi.d_scale != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(epi_dscale * __uint_as_float(v[i]));
+                }
             };
             // one chunk: registers -> swizzled staging box -> TMA store (or plain stores when C is not TMA-able)
             auto emit = [&](const uint32_t (&v)[32], int c) {
                 const int col0 = col_base + c * 32;
-                if (args.tma_store && args.epi.out_dtype != 0) {
+                if (args.tma_store && args.epi.out_dtype >= 3) {
+                    // 8-bit output: the box is 32 rows x 32 bytes, unswizzled
+                    if (issuer) ptx::bulk_wait_group_read<0>();
+                    __syncwarp();
+                    const uint32_t row_addr = sb + lane * 32;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            w[j] = pack8(__uint_as_float(v[16 * i + 4 * j]), __uint_as_float(v[16 * i + 4 * j + 1]),
+                                         __uint_as_float(v[16 * i + 4 * j + 2]), __uint_as_float(v[16 * i + 4 * j + 3]),
+                                         args.epi.out_dtype);
+                        ptx::st_shared_v4(row_addr + i * 16, w[0], w[1], w[2], w[3]);
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (issuer) {
+                        if (row0 < args.M && col0 < args.N) ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        ptx::bulk_commit_group();
+                    }
+                } else if (args.tma_store && args.epi.out_dtype != 0) {
                     // 16-bit output: the box is 32 rows x 64 bytes, unswizzled
                     if (issuer) ptx::bulk_wait_group_read<0>();
                     __syncwarp();
@@ -563,6 +632,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         if (issuer) ptx::bulk_wait_group<0>();                    // all stores of this warp are complete
         __syncwarp();
+        if (args.epi.amax != nullptr) amax_merge_warp(args.epi.amax, epi_amax);
     }
 
     // ---------------- teardown ----------------

@@ -104,6 +104,45 @@ def gemm_scaled(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: flo
     return d
 
 
+EPILOGUE_OUT_DTYPES = {**OUT_DTYPES, torch.float8_e4m3fn: 3, torch.float8_e5m2: 4}
+
+
+def gemm_epilogue(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: float = 1.0, beta: float = 0.0,
+                  a_scale: torch.Tensor | None = None, b_scale: torch.Tensor | None = None,
+                  d_scale: torch.Tensor | None = None, amax_d: torch.Tensor | None = None,
+                  bias: torch.Tensor | None = None, depth: int = 0, kernel: int = KERNEL_AUTO, split_k: int = 0,
+                  max_ctas: int = 0):
+    """t = alpha * a_scale * b_scale * (A B^T) + beta * D + bias[n];  amax_d = max |t|;  D = convert(d_scale * t).
+
+    The whole epilogue of the reference's cuBLASLt comparator (GEMM/src/cublas.cu:37-53; amax and scale slots in
+    GEMM/include/helper.h:59-66).  D may be float32, bfloat16, float16, float8_e4m3fn or float8_e5m2 (8-bit outputs
+    round to nearest even and saturate to finite).  Scales and amax_d are one-element float32 CUDA tensors; bias has
+    N elements of float32, bfloat16 or float16.
+    """
+    m, k = a.shape
+    n, k2 = b.shape
+    if k != k2 or d.shape != (m, n):
+        raise ValueError("shape mismatch")
+    if d.dtype not in EPILOGUE_OUT_DTYPES:
+        raise TypeError("d must be float32, bfloat16, float16, float8_e4m3fn or float8_e5m2")
+    for s_ in (a_scale, b_scale, d_scale, amax_d):
+        if s_ is not None and (s_.dtype != torch.float32 or not s_.is_cuda or s_.numel() != 1):
+            raise TypeError("scales and amax are one-element float32 CUDA tensors")
+    if bias is not None and (bias.dtype not in OUT_DTYPES or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous()):
+        raise TypeError("bias is a contiguous CUDA vector of N float32 / bfloat16 / float16 values")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    ep = _cabi.EpilogueDesc(ctypes.sizeof(_cabi.EpilogueDesc), float(alpha), float(beta), ptr(a_scale), ptr(b_scale),
+                            ptr(d_scale), ptr(amax_d), ptr(bias), OUT_DTYPES[bias.dtype] if bias is not None else 0)
+    opt = Options(ctypes.sizeof(Options), depth, kernel, split_k, max_ctas)
+    with torch.cuda.device(d.device):
+        rc = _cabi.lib().b200fp8_gemm_rowcol_epilogue(
+            m, k, n, a.data_ptr(), dtype_code(a), a.stride(0) if m > 1 else k, b.data_ptr(), dtype_code(b),
+            b.stride(0) if n > 1 else k, d.data_ptr(), EPILOGUE_OUT_DTYPES[d.dtype], d.stride(0) if m > 1 else n,
+            ctypes.byref(ep), ctypes.byref(opt), _stream_ptr(d.device))
+    _cabi.check(rc, "gemm_epilogue")
+    return d
+
+
 def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, depth: int = 0):
     """BmFN's whole sequence with HOST tensors (GEMM/gemm_main.cpp:56-64, :77, :161): upload, run, download."""
     if a.is_cuda or b.is_cuda or out.is_cuda:
