@@ -132,6 +132,36 @@ int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype
                                  const b200fp8_epilogue* epilogue, const b200fp8_options* options, void* stream);
 
 /*
+ * GEMV, SpMM and SpMV: the next kernels on the reference's roadmap (README.md:7, "GEMM,
+ * GEMV, SpMM, SpMV"); the reference ships only their input generators
+ * (GEMM/include/bm_test_utils.h:48-70 blocked-ELL column indices, :73-130 CSR) and no
+ * kernels, so these entry points have no counterpart to replace.
+ *
+ * b200fp8_gemv_f32:  y[n] = sum_k B[n][k] * x[k]  -- the operator with M = 1.
+ *
+ * Blocked-ELL sparse A, the format of GenerateUniformBlockedELLIndex
+ * (bm_test_utils.h:48-70) with 128 x 128 blocks: every block row (128 rows of A) stores
+ * `ell_blocks_per_row` blocks; `ell_values` is the compact row-major matrix
+ * [M][ell_blocks_per_row * 128] (pitch lda, 8-bit floats) and
+ * `ell_col_ind[ceil(M/128)][ell_blocks_per_row]` (DEVICE, int32) gives for each block the
+ * block column of A it occupies, i.e. columns [128*c, 128*c + 128) of K.  An index < 0 or
+ * beyond K marks a padding block that contributes nothing, whatever its values.  Blocks
+ * are accumulated in stored order.
+ *
+ * b200fp8_spmm_bell_rowcol_f32:  C[M][N] = A_sparse[M][K] * B[N][K]^T   (B, C as in the dense operator;
+ *                                options->kernel: AUTO, CTA1_N256 or CTA1_N128)
+ * b200fp8_spmv_bell_f32:         y[M]    = A_sparse[M][K] * x[K]
+ */
+int b200fp8_gemv_f32(int n, int k, const void* b, int b_dtype, long long ldb, const void* x, int x_dtype, float* y,
+                     void* stream);
+int b200fp8_spmm_bell_rowcol_f32(int m, int k, int n, const void* ell_values, int a_dtype, long long lda,
+                                 const int* ell_col_ind, int ell_blocks_per_row, const void* b, int b_dtype,
+                                 long long ldb, float* c, long long ldc, const b200fp8_options* options, void* stream);
+int b200fp8_spmv_bell_f32(int m, int k, const void* ell_values, int a_dtype, long long lda, const int* ell_col_ind,
+                          int ell_blocks_per_row, const void* x, int x_dtype, float* y, const b200fp8_options* options,
+                          void* stream);
+
+/*
  * N-sharded multi-GPU GEMM with the all-gather of C fused into the kernel's
  * epilogue (no counterpart in the reference, which is single-GPU; it follows
  * the operator above).  Rank `rank` of `world` (<= 8, one process per GPU)

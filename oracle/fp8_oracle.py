@@ -173,3 +173,43 @@ def check_tolerance(C: np.ndarray, C64: np.ndarray, S: np.ndarray, rel: float = 
 
 def max_threads() -> int:
     return int(lib().oracle_max_threads())
+
+
+# ---------------------------------------------------------------- blocked-ELL sparse operands
+
+BELL_BLOCK = 128
+
+
+def make_bell_uniform(m: int, k: int, blocks: int, fmt: int, seed: int, sigma: float = 1.0):
+    """A random blocked-ELL matrix with 128 x 128 blocks: (values [M][blocks*128] bytes, col_ind [ceil(M/128)][blocks]).
+
+    Column indices follow the distribution of the reference's GenerateUniformBlockedELLIndex
+    (GEMM/include/bm_test_utils.h:48-70): per block row a uniformly random subset of `blocks` of the
+    ceil(K/128) block columns, in ascending order.  (The reference draws it with std::random_shuffle,
+    whose random source is implementation-defined, so only the distribution can be restated.)"""
+    rng = np.random.default_rng(seed)
+    block_rows = (m + BELL_BLOCK - 1) // BELL_BLOCK
+    block_cols = (k + BELL_BLOCK - 1) // BELL_BLOCK
+    assert 0 <= blocks <= block_cols
+    col_ind = np.empty((block_rows, blocks), dtype=np.int32)
+    for r in range(block_rows):
+        col_ind[r] = np.sort(rng.choice(block_cols, size=blocks, replace=False))
+    values = fill_normal(m * blocks * BELL_BLOCK, fmt, sigma, seed + 1).reshape(m, blocks * BELL_BLOCK)
+    return values, col_ind
+
+
+def bell_to_dense(values: np.ndarray, col_ind: np.ndarray, k: int) -> np.ndarray:
+    """Dense [M][K] bytes of a blocked-ELL matrix; blocks with an index < 0 or beyond K are dropped, columns of a
+    block that reach past K are cut (what the kernels' zero-filled loads do).  Absent entries are +0 (byte 0)."""
+    m = values.shape[0]
+    dense = np.zeros((m, k), dtype=np.uint8)
+    for r in range(col_ind.shape[0]):
+        r0, r1 = r * BELL_BLOCK, min(m, (r + 1) * BELL_BLOCK)
+        for j, c in enumerate(col_ind[r]):
+            c0 = int(c) * BELL_BLOCK
+            if c < 0 or c0 >= k:
+                continue
+            w = min(BELL_BLOCK, k - c0)
+            assert not dense[r0:r1, c0:c0 + w].any(), "duplicate block column in a block row"
+            dense[r0:r1, c0:c0 + w] = values[r0:r1, j * BELL_BLOCK:j * BELL_BLOCK + w]
+    return dense

@@ -29,6 +29,9 @@ DECLARED_SYMBOLS = (
     "b200fp8_gemm_rowcol_f32_ex",
     "b200fp8_gemm_rowcol_scaled",
     "b200fp8_gemm_rowcol_epilogue",
+    "b200fp8_gemv_f32",
+    "b200fp8_spmm_bell_rowcol_f32",
+    "b200fp8_spmv_bell_f32",
     "b200fp8_gemm_rowcol_f32_allgather",
     "b200fp8_gemm_rowcol_f32_host",
     "b200fp8_gemm_rowcol_f32_noalloc",
@@ -92,6 +95,10 @@ def lib() -> ctypes.CDLL:
                                                  ctypes.c_float, vp, vp, ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_epilogue.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ci, ll,
                                                    ctypes.POINTER(EpilogueDesc), ctypes.POINTER(Options), vp]
+        L.b200fp8_gemv_f32.argtypes = [ci, ci, vp, ci, ll, vp, ci, vp, vp]
+        L.b200fp8_spmm_bell_rowcol_f32.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, vp, ci, ll, vp, ll,
+                                                   ctypes.POINTER(Options), vp]
+        L.b200fp8_spmv_bell_f32.argtypes = [ci, ci, vp, ci, ll, vp, ci, vp, ci, vp, ctypes.POINTER(Options), vp]
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
         L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
         L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]

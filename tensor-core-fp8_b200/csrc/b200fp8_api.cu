@@ -120,12 +120,19 @@ struct Tune {
 const Tune& tune() { static Tune t; return t; }
 long long* g_trace = nullptr;   // diagnostics buffer (B200FP8_DEBUG & 64)
 
+// Blocked-ELL description of A (128 x 128 blocks): column-block indices [ceil(M/128)][blocks] on the device
+struct EllSpec {
+    const int* col_ind;
+    int blocks;
+};
+
 template <int BN, int STAGES, int CTAS, int NACC>
 cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
-                        const PeerSet* peers, const Epilogue* epi, cudaStream_t stream) {
+                        const PeerSet* peers, const Epilogue* epi, cudaStream_t stream, const EllSpec* ell = nullptr) {
     using L = GemmSmem<BN, STAGES, CTAS, NACC>;
     static bool attr_done[kMaxDevices] = {};
+    if (ell && CTAS != 1) return cudaErrorInvalidValue;       // a block row is one 128-row M-tile
     auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC>;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -136,7 +143,12 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     }
     GemmArgs args{};
     args.M = m; args.N = n; args.K = k;
-    args.num_k_blocks = (k + kBlockK - 1) / kBlockK;
+    args.num_k_blocks = ell ? ell->blocks : (k + kBlockK - 1) / kBlockK;
+    if (ell) {
+        args.ell_col_ind = ell->col_ind;
+        args.ell_oob_a = ell->blocks * kBlockK;
+        args.ell_oob_b = (k + kBlockK - 1) / kBlockK * kBlockK;
+    }
     args.m_tiles = (m + kTileM * CTAS - 1) / (kTileM * CTAS);
     args.n_tiles = (n + L::kTileN - 1) / L::kTileN;
     args.group_m = (CTAS == 2) ? tune().group_m_pair : tune().group_m_single;
@@ -168,7 +180,8 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
 
     CUtensorMap ta, tb, tc;
     cudaError_t e;
-    if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, k, m, lda, kBlockK, kTileM)) != cudaSuccess) return e;
+    const long long a_cols = ell ? static_cast<long long>(ell->blocks) * kBlockK : k;
+    if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, a_cols, m, lda, kBlockK, kTileM)) != cudaSuccess) return e;
     if ((e = encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows)) != cudaSuccess) return e;
     if (args.tma_store && out_bytes == 1) {
         if ((e = encode_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, c, n, m, ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != cudaSuccess) return e;
@@ -228,13 +241,17 @@ bool valid_dtype(int d) { return d == B200FP8_E4M3 || d == B200FP8_E5M2; }
 
 cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
                           long long ldb, float* c, long long ldc, const b200fp8_options* opt, cudaStream_t stream,
-                          const PeerSet* peers = nullptr, const Epilogue* epi = nullptr) {
+                          const PeerSet* peers = nullptr, const Epilogue* epi = nullptr, const EllSpec* ell = nullptr) {
     if (m < 0 || n < 0 || k < 0 || !valid_dtype(a_dtype) || !valid_dtype(b_dtype)) return cudaErrorInvalidValue;
+    if (ell && (ell->blocks < 0 || ell->blocks > (1 << 20) ||
+                (ell->blocks > 0 && (!ell->col_ind || (reinterpret_cast<uintptr_t>(ell->col_ind) % 4)))))
+        return cudaErrorInvalidValue;
     if (m == 0 || n == 0) return cudaSuccess;
     if (!c || ldc < n) return cudaErrorInvalidValue;
     if (epi && epi->active && k == 0) return cudaErrorInvalidValue;   // the extended form needs a non-empty K
-    if (k == 0) return cudaMemset2DAsync(c, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(n) * 4, m, stream);
-    if (!a || !b || lda < k || ldb < k) return cudaErrorInvalidValue;
+    if (k == 0 || (ell && ell->blocks == 0))
+        return cudaMemset2DAsync(c, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(n) * 4, m, stream);
+    if (!a || !b || lda < (ell ? static_cast<long long>(ell->blocks) * kBlockK : k) || ldb < k) return cudaErrorInvalidValue;
     if ((k % 16) || (lda % 16) || (ldb % 16)) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(a) % 16) || (reinterpret_cast<uintptr_t>(b) % 16) ||
         (reinterpret_cast<uintptr_t>(c) % (epi ? out_dtype_bytes(epi->out_dtype) : 4)))
@@ -256,7 +273,8 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
         const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
         const long long wide_tiles = static_cast<long long>((m + 255) / 256) * ((n + 511) / 512);
-        if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
+        if (ell) kernel = n256_tiles >= ctx->sm_count / 2 ? B200FP8_KERNEL_CTA1_N256 : B200FP8_KERNEL_CTA1_N128;
+        else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
         // long runs are power-limited: the wide tile moves a quarter less data per flop
         else if (wide_tiles >= 16LL * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N512;
         else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
@@ -264,11 +282,12 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
     if (kernel == B200FP8_KERNEL_SKINNY && m > kSkinnyMaxM) return cudaErrorInvalidValue;
+    if (ell && kernel != B200FP8_KERNEL_CTA1_N256 && kernel != B200FP8_KERNEL_CTA1_N128) return cudaErrorInvalidValue;
     if (peers && (peers->count > 0 || peers->multicast) && kernel == B200FP8_KERNEL_SKINNY) kernel = B200FP8_KERNEL_PAIR_N256;
 
 #define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
 #define B200FP8_LAUNCH4(BN, ST, CT, NA) \
-    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream)
+    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);
@@ -363,6 +382,52 @@ int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype
         if (e != cudaSuccess) return e;
     }
     return gemm_dispatch(m, k, n, a, a_dtype, lda, b, b_dtype, ldb, static_cast<float*>(d), ldd, options, st, nullptr, &epi);
+}
+
+int b200fp8_gemv_f32(int n, int k, const void* b, int b_dtype, long long ldb, const void* x, int x_dtype, float* y,
+                     void* stream) {
+    // y[n] = sum_k B[n][k] x[k]: the operator with M = 1 (x is the single row of A), HBM-bound split-K kernel
+    return gemm_dispatch(1, k, n, x, x_dtype, k, b, b_dtype, ldb, y, n, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp8_spmm_bell_rowcol_f32(int m, int k, int n, const void* ell_values, int a_dtype, long long lda,
+                                 const int* ell_col_ind, int ell_blocks_per_row, const void* b, int b_dtype,
+                                 long long ldb, float* c, long long ldc, const b200fp8_options* options, void* stream) {
+    if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
+    if (k <= 0) return cudaErrorInvalidValue;
+    EllSpec ell{ell_col_ind, ell_blocks_per_row};
+    return gemm_dispatch(m, k, n, ell_values, a_dtype, lda, b, b_dtype, ldb, c, ldc, options,
+                         static_cast<cudaStream_t>(stream), nullptr, nullptr, &ell);
+}
+
+int b200fp8_spmv_bell_f32(int m, int k, const void* ell_values, int a_dtype, long long lda, const int* ell_col_ind,
+                          int ell_blocks_per_row, const void* x, int x_dtype, float* y, const b200fp8_options* options,
+                          void* stream) {
+    // y[m] = sum_k A[m][k] x[k] with A in blocked-ELL form: the split-K kernel with the roles swapped -- the sparse
+    // matrix is the large, streamed operand (its block rows are the kernel's 128-row tiles), x the single small row
+    if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
+    if (m < 0 || k <= 0 || ell_blocks_per_row < 0 || ell_blocks_per_row > (1 << 20) || !valid_dtype(a_dtype) ||
+        !valid_dtype(x_dtype))
+        return cudaErrorInvalidValue;
+    if (m == 0) return cudaSuccess;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!y) return cudaErrorInvalidValue;
+    if (ell_blocks_per_row == 0) return cudaMemsetAsync(y, 0, static_cast<size_t>(m) * sizeof(float), st);
+    const long long width = static_cast<long long>(ell_blocks_per_row) * kBlockK;
+    if (!ell_values || !ell_col_ind || !x || lda < width || (lda % 16) || (k % 16)) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(ell_values) % 16) || (reinterpret_cast<uintptr_t>(x) % 16) ||
+        (reinterpret_cast<uintptr_t>(y) % 4) || (reinterpret_cast<uintptr_t>(ell_col_ind) % 4))
+        return cudaErrorInvalidValue;
+    const int depth = options ? options->depth : 0;
+    const int split_k = options ? options->split_k : 0;
+    if ((depth != 0 && depth != 2 && depth != 4) || split_k < 0) return cudaErrorInvalidValue;
+    DeviceCtx* ctx = nullptr;
+    cudaError_t e = get_ctx(&ctx);
+    if (e != cudaSuccess) return e;
+    e = launch_skinny(ctx->sm_count, ctx->status, g_encode, 1, static_cast<int>(width), m, x, k, ell_values, lda, y, m,
+                      x_dtype, a_dtype, depth, split_k, nullptr, st, ell_col_ind, k);
+    if (e == cudaSuccess) ++t_launches;
+    return e;
 }
 
 int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, int a_dtype, const void* b_shard,

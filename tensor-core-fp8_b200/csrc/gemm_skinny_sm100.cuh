@@ -39,6 +39,11 @@ struct SkinnyArgs {
     float* C;
     long long ldc;
     int* status;
+    // Blocked-ELL form of the LARGE operand B (128 x 128 blocks): tmap_b describes the compact values matrix
+    // [N][kb_total * 128], and k-block kb of N-tile nt multiplies the columns [col * 128, col * 128 + 128) of A with
+    // col = ell_col_ind[nt * kb_total + kb]; col < 0 or beyond K is a padding block (zeros are loaded for both).
+    const int* ell_col_ind;
+    int ell_oob_a, ell_oob_b;   // 128-aligned k coordinates beyond A's K / beyond the compact B
     Epilogue epi;        // extended epilogue (alpha, beta, scales, 16-bit output); inactive for the plain operator
 };
 
@@ -132,17 +137,35 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         uint32_t ph = 0;
         int issued = 0;
         bool ok = true;
+        // blocked-ELL B: lane l holds the column block of k-block (chunk base + l); the next 32 are prefetched
+        const int* ell_row = nullptr;
+        int ell_cur = -1, ell_nxt = -1;
+        if (args.ell_col_ind != nullptr) {
+            ell_row = args.ell_col_ind + static_cast<long long>(n_tile) * args.kb_total;
+            if (kb0 + lane < kb1) ell_nxt = ell_row[kb0 + lane];
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
             if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, false)) {
                 record_failure(args.status, abort_flag, kStatusSkinnyTimeout);
                 ok = false;
                 break;
             }
+            int ka = kb * kBlockK, kbx = kb * kBlockK;               // k coordinates of the A and B boxes
+            if (ell_row != nullptr) {
+                const int rel = kb - kb0;
+                if ((rel & 31) == 0) {
+                    ell_cur = ell_nxt;
+                    ell_nxt = (kb + 32 + lane < kb1) ? ell_row[kb + 32 + lane] : -1;
+                }
+                const int col = __shfl_sync(0xffffffffu, ell_cur, rel & 31);
+                if (col < 0 || col >= args.ell_oob_a / kBlockK) { ka = args.ell_oob_a; kbx = args.ell_oob_b; }
+                else ka = col * kBlockK;
+            }
             const uint32_t b_dst = smem_base + s * L::kStageBytes;
             if (ptx::elect_one()) {
                 ptx::mbar_arrive_expect_tx(bar_full + 8 * s, L::kStageBytes);
-                ptx::tma_load_2d(b_dst, &tmap_b, kb * kBlockK, n0, bar_full + 8 * s);
-                ptx::tma_load_2d(b_dst + L::kBBytes, &tmap_a, kb * kBlockK, 0, bar_full + 8 * s);
+                ptx::tma_load_2d(b_dst, &tmap_b, kbx, n0, bar_full + 8 * s);
+                ptx::tma_load_2d(b_dst + L::kBBytes, &tmap_a, ka, 0, bar_full + 8 * s);
             }
             __syncwarp();
             ++issued;
@@ -345,7 +368,10 @@ cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const
 
 inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, int m, int k, int n, const void* a,
                                  long long lda, const void* b, long long ldb, float* c, long long ldc, int a_dtype,
-                                 int b_dtype, int depth, int split_k, const Epilogue* epi, cudaStream_t stream) {
+                                 int b_dtype, int depth, int split_k, const Epilogue* epi, cudaStream_t stream,
+                                 const int* ell_col_ind = nullptr, int ell_k_small = 0) {
+    // With ell_col_ind the large operand B is in blocked-ELL form: `k` is the width of its compact values matrix
+    // (blocks per row x 128) and ell_k_small the K of the small operand A.
     const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
     const int n_tiles = (n + kSkinnyTileN - 1) / kSkinnyTileN;
     if (n_tiles > 65535 * 32) return cudaErrorInvalidValue;
@@ -358,10 +384,15 @@ inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, 
     args.C = c; args.ldc = ldc;
     args.status = status;
     if (epi) args.epi = *epi;
+    if (ell_col_ind) {
+        args.ell_col_ind = ell_col_ind;
+        args.ell_oob_a = (ell_k_small + kBlockK - 1) / kBlockK * kBlockK;
+        args.ell_oob_b = args.kb_total * kBlockK;
+    }
     CUtensorMap tb, ta;
     cudaError_t e;
     if ((e = skinny_encode(enc, &tb, b, k, n, ldb, kSkinnyTileN)) != cudaSuccess) return e;
-    if ((e = skinny_encode(enc, &ta, a, k, m, lda, mp)) != cudaSuccess) return e;
+    if ((e = skinny_encode(enc, &ta, a, ell_col_ind ? ell_k_small : k, m, lda, mp)) != cudaSuccess) return e;
     switch (mp) {
         case 16: return launch_skinny_mp<16>(tb, ta, args, n_tiles, stream);
         case 32: return launch_skinny_mp<32>(tb, ta, args, n_tiles, stream);

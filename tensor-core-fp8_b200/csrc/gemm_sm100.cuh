@@ -134,6 +134,12 @@ struct GemmArgs {
     // Fused all-gather of C (N-sharded multi-GPU run): every finished box is also stored, with plain
     // 16-byte stores over NVLink, into the same position of the C matrix of each peer GPU.
     // peer_c[p] points at this rank's column block inside peer p's full matrix (row pitch ldc).
+    // Blocked-ELL sparse A (CTAS == 1 only; block = 128 rows x 128 columns = one M-tile x one k-block): tmap_a
+    // describes the compact values matrix [M][num_k_blocks * 128], and k-block kb of M-tile mt multiplies the
+    // columns [col * 128, col * 128 + 128) of B with col = ell_col_ind[mt * num_k_blocks + kb]; col < 0 is a
+    // padding block that contributes nothing (both operands are then loaded from outside the matrices: zeros).
+    const int* ell_col_ind;
+    int ell_oob_a, ell_oob_b;     // 128-aligned k coordinates beyond the compact A / beyond B's K
     Epilogue epi;
     int num_peers;
     float* peer_c[kMaxPeers];
@@ -324,11 +330,28 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     __nanosleep(256);
                 __syncwarp();
             }
+            // blocked-ELL A: lane l holds the column block of k-block (chunk base + l); the next 32 are prefetched
+            const int* ell_row = nullptr;
+            int ell_cur = -1, ell_nxt = -1;
+            if (CTAS == 1 && args.ell_col_ind != nullptr) {
+                ell_row = args.ell_col_ind + static_cast<long long>(m0 / kTileM) * nkb;
+                if (lane < nkb) ell_nxt = ell_row[lane];
+            }
             for (int kb = 0; kb < nkb; ++kb) {
                 if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusProducerTimeout);
                     ok = false;
                     break;
+                }
+                int ka = kb * kBlockK, kbx = kb * kBlockK;           // k coordinates of the A and B boxes
+                if (CTAS == 1 && ell_row != nullptr) {
+                    if ((kb & 31) == 0) {
+                        ell_cur = ell_nxt;
+                        ell_nxt = (kb + 32 + lane < nkb) ? ell_row[kb + 32 + lane] : -1;
+                    }
+                    const int col = __shfl_sync(0xffffffffu, ell_cur, kb & 31);
+                    if (col < 0 || col >= args.ell_oob_b / kBlockK) { ka = args.ell_oob_a; kbx = args.ell_oob_b; }
+                    else kbx = col * kBlockK;
                 }
                 const uint32_t a_dst = smem_base + L::kRingOff + s * L::kStageBytes;
                 const uint32_t b_dst = a_dst + L::kABytes;
@@ -340,16 +363,16 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
                     } else if (pair) {
                         if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
-                        ptx::tma_load_2d_pair(a_dst, &tmap_a, kb * kBlockK, m0, full0 + 8 * s);
+                        ptx::tma_load_2d_pair(a_dst, &tmap_a, ka, m0, full0 + 8 * s);
 #pragma unroll
                         for (int j = 0; j < NACC; ++j)
-                            ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kb * kBlockK, nb0 + j * BN, full0 + 8 * s);
+                            ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, full0 + 8 * s);
                     } else {
                         ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
-                        ptx::tma_load_2d(a_dst, &tmap_a, kb * kBlockK, m0, bar_full + 8 * s);
+                        ptx::tma_load_2d(a_dst, &tmap_a, ka, m0, bar_full + 8 * s);
 #pragma unroll
                         for (int j = 0; j < NACC; ++j)
-                            ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kb * kBlockK, nb0 + j * BN, bar_full + 8 * s);
+                            ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, bar_full + 8 * s);
                     }
                 }
                 __syncwarp();

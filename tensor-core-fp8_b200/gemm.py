@@ -143,6 +143,66 @@ def gemm_epilogue(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: f
     return d
 
 
+ELL_BLOCK = 128     # rows and columns of a blocked-ELL block
+
+
+def gemv(b: torch.Tensor, x: torch.Tensor, y: torch.Tensor):
+    """y[n] = sum_k B[n][k] x[k]: the GEMV of the reference's roadmap (README.md:7) = the operator with M = 1."""
+    n, k = b.shape
+    if x.numel() != k or y.numel() != n or y.dtype != torch.float32 or not (x.is_contiguous() and y.is_contiguous()):
+        raise ValueError("x has K elements, y has N float32 elements, both contiguous")
+    with torch.cuda.device(y.device):
+        rc = _cabi.lib().b200fp8_gemv_f32(n, k, b.data_ptr(), dtype_code(b), b.stride(0) if n > 1 else k, x.data_ptr(),
+                                           dtype_code(x), y.data_ptr(), _stream_ptr(y.device))
+    _cabi.check(rc, f"gemv n={n} k={k}")
+    return y
+
+
+def _check_bell(values: torch.Tensor, col_ind: torch.Tensor, m: int):
+    if col_ind.dtype != torch.int32 or not col_ind.is_cuda or not col_ind.is_contiguous() or col_ind.dim() != 2:
+        raise TypeError("col_ind is a contiguous int32 CUDA matrix [ceil(M/128)][blocks per row]")
+    blocks = col_ind.shape[1]
+    if col_ind.shape[0] != (m + ELL_BLOCK - 1) // ELL_BLOCK or values.shape[1] != blocks * ELL_BLOCK:
+        raise ValueError("values is [M][blocks * 128], col_ind is [ceil(M/128)][blocks]")
+    return blocks
+
+
+def spmm_bell(values: torch.Tensor, col_ind: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, depth: int = 0,
+              kernel: int = KERNEL_AUTO, max_ctas: int = 0):
+    """C = A_sparse B^T with A in blocked-ELL form, 128 x 128 blocks (the format of GenerateUniformBlockedELLIndex,
+    GEMM/include/bm_test_utils.h:48-70): values [M][blocks * 128] FP8, col_ind [ceil(M/128)][blocks] int32
+    block-column indices (negative = padding block), b [N][K] FP8, out [M][N] float32."""
+    m = values.shape[0]
+    n, k = b.shape
+    blocks = _check_bell(values, col_ind, m)
+    if out.shape != (m, n) or out.dtype != torch.float32:
+        raise ValueError("out is [M][N] float32")
+    opt = Options(ctypes.sizeof(Options), depth, kernel, 0, max_ctas)
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().b200fp8_spmm_bell_rowcol_f32(
+            m, k, n, values.data_ptr(), dtype_code(values), values.stride(0) if m > 1 else blocks * ELL_BLOCK,
+            col_ind.data_ptr(), blocks, b.data_ptr(), dtype_code(b), b.stride(0) if n > 1 else k, out.data_ptr(),
+            out.stride(0) if m > 1 else n, ctypes.byref(opt), _stream_ptr(out.device))
+    _cabi.check(rc, f"spmm_bell m={m} k={k} n={n} blocks={blocks}")
+    return out
+
+
+def spmv_bell(values: torch.Tensor, col_ind: torch.Tensor, x: torch.Tensor, y: torch.Tensor, *, split_k: int = 0):
+    """y = A_sparse x with A in blocked-ELL form as in spmm_bell; x has K FP8 elements, y has M float32 elements."""
+    m = values.shape[0]
+    k = x.numel()
+    blocks = _check_bell(values, col_ind, m)
+    if y.numel() != m or y.dtype != torch.float32 or not (x.is_contiguous() and y.is_contiguous()):
+        raise ValueError("y has M float32 elements; x and y are contiguous")
+    opt = Options(ctypes.sizeof(Options), 0, KERNEL_AUTO, split_k, 0)
+    with torch.cuda.device(y.device):
+        rc = _cabi.lib().b200fp8_spmv_bell_f32(
+            m, k, values.data_ptr(), dtype_code(values), values.stride(0) if m > 1 else blocks * ELL_BLOCK,
+            col_ind.data_ptr(), blocks, x.data_ptr(), dtype_code(x), y.data_ptr(), ctypes.byref(opt), _stream_ptr(y.device))
+    _cabi.check(rc, f"spmv_bell m={m} k={k} blocks={blocks}")
+    return y
+
+
 def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, depth: int = 0):
     """BmFN's whole sequence with HOST tensors (GEMM/gemm_main.cpp:56-64, :77, :161): upload, run, download."""
     if a.is_cuda or b.is_cuda or out.is_cuda:
