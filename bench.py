@@ -46,6 +46,13 @@ WORKLOADS = {
     "skinny128": (128, 8192, 8192, False),
     "skinny_wide": (32, 8192, 57344, False),
 }
+# Sparse workloads (blocked-ELL A, 128 x 128 blocks; one GPU): name -> (op, M, K, N, stored blocks per block row)
+SPARSE_WORKLOADS = {
+    "spmm8192_d25": ("spmm", 8192, 8192, 8192, 16),      # a quarter of the 64 block columns
+    "spmm8192_d100": ("spmm", 8192, 8192, 8192, 64),     # every block stored: the table lookup's overhead
+    "spmv16384_d25": ("spmv", 16384, 16384, 1, 32),
+    "gemv16384": ("gemv", 1, 16384, 16384, 0),
+}
 SEED_BASE = 0xB200F800
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
@@ -152,7 +159,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    M, K, N, sharded = WORKLOADS[args.workload]
+    if args.workload in SPARSE_WORKLOADS:       # the CPU loop has no sparse form: the dense problem of the same shape
+        M, K, N, sharded = SPARSE_WORKLOADS[args.workload][1:4] + (False,)
+    else:
+        M, K, N, sharded = WORKLOADS[args.workload]
     # bounded sample per step: about a second of work per step on all host threads
     rates = []
     for i in range(args.warmup + args.steps):
@@ -178,13 +188,105 @@ def run_reference(args):
     return 0
 
 
+def run_sparse(args, g, torch, dev, json_fd):
+    """GEMV / blocked-ELL SpMM / SpMV on one GPU: all steps in one CUDA graph over rotating operand sets larger than
+    L2; FLOPs and bytes count the STORED blocks only (algorithmic work of the sparse problem)."""
+    op, M, K, N, blocks = SPARSE_WORKLOADS[args.workload]
+    f8 = torch.float8_e4m3fn
+    width = blocks * 128
+    gen = torch.Generator(device=dev).manual_seed(SEED_BASE & 0x7FFFFFFF)
+    if op == "gemv":
+        set_bytes = N * K
+    else:
+        set_bytes = M * width + (N * K + 4 * M * N if op == "spmm" else 0)
+    nsets = max(2, min(8, (1 << 30) // set_bytes))
+    sets = []
+    for i in range(nsets):
+        if op == "gemv":
+            b = torch.empty((N, K), dtype=f8, device=dev)
+            g.fill_normal(b, 1.0, SEED_BASE + 80 + i)
+            sets.append((b, torch.empty(N, dtype=torch.float32, device=dev)))
+            continue
+        vals = torch.empty((M, width), dtype=f8, device=dev)
+        g.fill_normal(vals, 1.0, SEED_BASE + 80 + i)
+        ind = torch.rand((M // 128, K // 128), generator=gen, device=dev).argsort(dim=1)[:, :blocks].sort(dim=1).values.int().contiguous()
+        if op == "spmm":
+            b = torch.empty((N, K), dtype=f8, device=dev)
+            g.fill_normal(b, 1.0, SEED_BASE + 90 + i)
+            sets.append((vals, ind, b, torch.empty((M, N), dtype=torch.float32, device=dev)))
+        else:
+            sets.append((vals, ind, torch.empty(M, dtype=torch.float32, device=dev)))
+    x = torch.empty(K, dtype=f8, device=dev)
+    g.fill_normal(x, 1.0, SEED_BASE + 99)
+
+    def step(i):
+        t = sets[i % nsets]
+        if op == "spmm":
+            g.spmm_bell(t[0], t[1], t[2], t[3], kernel=args.kernel, depth=args.depth)
+        elif op == "spmv":
+            g.spmv_bell(t[0], t[1], x, t[2])
+        else:
+            g.gemv(t[0], x, t[1])
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    launches0 = g.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            step(i)
+    launches = g.launch_count() - launches0
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(dev.index)) as clk:
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    if g.device_status() != 0:
+        raise SystemExit("device status word is non-zero: a kernel's bounded wait ran out")
+    ms = e0.elapsed_time(e1) / args.steps
+    peaks = measured_peaks()
+    if op == "spmm":
+        flops = 2.0 * M * N * width
+        nbytes = float(M * width + N * K + 4 * M * N + 4 * (M // 128) * blocks)
+    elif op == "spmv":
+        flops = 2.0 * M * width
+        nbytes = float(M * width + K + 4 * M + 4 * (M // 128) * blocks)
+    else:
+        flops = 2.0 * N * K
+        nbytes = float(N * K + K + 4 * N)
+    tflops = flops / (ms * 1e-3) / 1e12
+    if op == "spmm":
+        peak = 2.0 * peaks["bf16_sustained"]
+        roof = {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                "peak_source": peaks["source"] + ": 2 x sustained cuBLAS bf16", "traffic": None}
+    else:
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                "peak_source": peaks["source"] + " (copy bandwidth)", "traffic": None}
+    roof.update({"algorithmic_bytes": nbytes, "algorithmic_flops": flops, "kernel_ms": ms})
+    line = {"metric": "fp8_gemm_tflops", "value": tflops, "unit": "TFLOPS", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8", "data": "synthetic",
+            "config": {"workload": args.workload, "op": op, "M": M, "K": K, "N": N, "ell_block": 128,
+                       "stored_blocks_per_block_row": blocks, "block_columns": K // 128, "a": "e4m3", "b": "e4m3",
+                       "out": "f32", "l2": f"rotating over {nsets} distinct operand sets larger than L2",
+                       "timing": "one CUDA graph of all steps, replayed", "flops": "stored blocks only"},
+            "roofline": roof, "gpu_launches": int(launches), "clocks": clk.summary(), "e2e": None, "cpu_baseline": None}
+    os.write(json_fd, (json.dumps(line) + "\n").encode())
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="shard32768", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="shard32768", choices=sorted(WORKLOADS) + sorted(SPARSE_WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -225,6 +327,10 @@ def main() -> int:
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.workload in SPARSE_WORKLOADS:
+        if world > 1:
+            raise SystemExit("the sparse workloads run on one GPU")
+        return run_sparse(args, g, torch, dev, json_fd)
     if world > 1:
         # keep stdout to the one JSON line: NCCL prints its version banner there at NCCL_DEBUG=VERSION
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
