@@ -1,10 +1,10 @@
 """Regenerates the fixtures in this directory from the REFERENCE's own code.
 
-Needs the reference tree (default /root/reference) and the CUDA toolkit
+Needs the reference tree (--ref, default: the REF default of oracle/Makefile) and the CUDA toolkit
 headers; it is run once where those exist and its outputs are committed, so the
 tests themselves never touch the reference tree.
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference checkout>]
 
 What it records:
 
