@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
 
 #include "../../include/b200fp8.h"
@@ -106,7 +107,11 @@ struct Tune {
     int pace_limit_ns = 30000;
     int store_gap_ns = 0;
     int split_tail = 1;
+    int host_block_m = 4096;      // host-pointer entry: edge of the C blocks it pipelines over (rows / columns)
+    int host_block_n = 4096;
     Tune() {
+        if (const char* v = getenv("B200FP8_HOST_BLOCK_M")) host_block_m = atoi(v) >= 256 ? atoi(v) : host_block_m;
+        if (const char* v = getenv("B200FP8_HOST_BLOCK_N")) host_block_n = atoi(v) >= 256 ? atoi(v) : host_block_n;
         if (const char* v = getenv("B200FP8_SPLIT_TAIL")) split_tail = atoi(v);
         if (const char* v = getenv("B200FP8_STORE_GAP_NS")) store_gap_ns = atoi(v);
         if (const char* v = getenv("B200FP8_PACE_MIN_WAVES")) pace_min_waves = atoi(v);
@@ -471,65 +476,80 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     float* dc = static_cast<float*>(ctx->host_c);
     const uint8_t* db = static_cast<const uint8_t*>(ctx->host_b);
 
-    // Pipeline over blocks of C so that uploads, the operator and the download of C overlap on three
-    // streams.  The smaller operand goes up whole first; the other one is streamed block by block:
-    //   n <= m : B first, then row blocks of A -> row blocks of C (contiguous downloads)
-    //   n >  m : A first, then column blocks of B / C (what a wide, short problem wants)
-    const bool by_rows = n <= m;
-    const int extent = by_rows ? m : n;
-    int blocks = 1;
-    if (static_cast<double>(m) * n * k > 1e11 && extent >= 2048) blocks = 8;
-    int step = ((extent + blocks - 1) / blocks + 255) / 256 * 256;
-    if (step <= 0) step = extent;
-    blocks = (extent + step - 1) / step;
-    constexpr int kMaxBlocks = 64;
-    if (blocks > kMaxBlocks) return cudaErrorInvalidValue;
-    cudaEvent_t up[kMaxBlocks], done[kMaxBlocks];
-    for (int j = 0; j < blocks; ++j) {
-        cudaEventCreateWithFlags(&up[j], cudaEventDisableTiming);
-        cudaEventCreateWithFlags(&done[j], cudaEventDisableTiming);
-    }
+    // Pipeline over a grid of C blocks so that uploads, the operator and the download of C overlap on three
+    // streams.  C is the largest of the three matrices (4 bytes per element), so the call is bound by the
+    // download of C and the goal is to start it as early as possible: operands go up in row blocks of A and
+    // of B alternately (A0, B0, B1, A1, B2, A2, ...), and every C block is computed and sent down as soon as
+    // its two operand blocks have arrived.  The first block needs 2 of the 2 x 8 uploads instead of a whole
+    // operand, and the number of computable blocks grows quadratically while downloads drain them linearly.
+    auto split = [](int extent, int want, int* step) {
+        int blocks = want < 1 ? 1 : want;
+        int st = ((extent + blocks - 1) / blocks + 255) / 256 * 256;
+        if (st <= 0) st = extent;
+        *step = st;
+        return (extent + st - 1) / st;
+    };
+    constexpr int kMaxSide = 8;
+    const bool big = static_cast<double>(m) * n * k > 1e11;
+    int step_m = m, step_n = n;
+    auto side = [&](int extent, int edge) { return extent < 2048 ? 1 : std::min(kMaxSide, (extent + edge - 1) / edge); };
+    const int bm = big ? split(m, side(m, tune().host_block_m), &step_m) : 1;
+    const int bn = big ? split(n, side(n, tune().host_block_n), &step_n) : 1;
+    if (bm > kMaxSide || bn > kMaxSide) return cudaErrorInvalidValue;
+    cudaEvent_t up_a[kMaxSide], up_b[kMaxSide], done[kMaxSide * kMaxSide];
+    for (int i = 0; i < bm; ++i) cudaEventCreateWithFlags(&up_a[i], cudaEventDisableTiming);
+    for (int j = 0; j < bn; ++j) cudaEventCreateWithFlags(&up_b[j], cudaEventDisableTiming);
+    for (int t = 0; t < bm * bn; ++t) cudaEventCreateWithFlags(&done[t], cudaEventDisableTiming);
     b200fp8_options opt{};
     opt.struct_bytes = sizeof(opt);
     opt.depth = depth;
     cudaError_t first = cudaSuccess;
     auto keep = [&](cudaError_t x) { if (first == cudaSuccess && x != cudaSuccess) first = x; };
     uint8_t* da = static_cast<uint8_t*>(ctx->host_a);
+    uint8_t* dbw = static_cast<uint8_t*>(ctx->host_b);
     const uint8_t* ha = static_cast<const uint8_t*>(a_host);
     const uint8_t* hb = static_cast<const uint8_t*>(b_host);
-    if (by_rows) {
-        if (b_bytes) keep(cudaMemcpyAsync(ctx->host_b, hb, b_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
-    } else {
-        if (a_bytes) keep(cudaMemcpyAsync(da, ha, a_bytes, cudaMemcpyHostToDevice, ctx->copy_in));
-    }
-    for (int j = 0; j < blocks && first == cudaSuccess; ++j) {
-        const int x0 = j * step, xx = (extent - x0 < step) ? extent - x0 : step;
-        const size_t off = static_cast<size_t>(x0) * k;
-        if (k) {
-            if (by_rows) keep(cudaMemcpyAsync(da + off, ha + off, static_cast<size_t>(xx) * k, cudaMemcpyHostToDevice, ctx->copy_in));
-            else keep(cudaMemcpyAsync(const_cast<uint8_t*>(db) + off, hb + off, static_cast<size_t>(xx) * k, cudaMemcpyHostToDevice, ctx->copy_in));
-        }
-        keep(cudaEventRecord(up[j], ctx->copy_in));
-        keep(cudaStreamWaitEvent(ctx->compute, up[j], 0));
-        if (by_rows) {
-            float* cblk = dc + static_cast<size_t>(x0) * n;
-            keep(gemm_dispatch(xx, k, n, da + off, a_dtype, k, db, b_dtype, k, cblk, n, &opt, ctx->compute));
-            keep(cudaEventRecord(done[j], ctx->compute));
-            keep(cudaStreamWaitEvent(ctx->copy_out, done[j], 0));
-            keep(cudaMemcpyAsync(c_host + static_cast<size_t>(x0) * n, cblk, static_cast<size_t>(xx) * n * 4,
-                                 cudaMemcpyDeviceToHost, ctx->copy_out));
-        } else {
-            keep(gemm_dispatch(m, k, xx, da, a_dtype, k, db + off, b_dtype, k, dc + x0, n, &opt, ctx->compute));
-            keep(cudaEventRecord(done[j], ctx->compute));
-            keep(cudaStreamWaitEvent(ctx->copy_out, done[j], 0));
-            keep(cudaMemcpy2DAsync(c_host + x0, static_cast<size_t>(n) * 4, dc + x0, static_cast<size_t>(n) * 4,
-                                   static_cast<size_t>(xx) * 4, m, cudaMemcpyDeviceToHost, ctx->copy_out));
+    auto rows_of = [](int idx, int step, int extent) { return extent - idx * step < step ? extent - idx * step : step; };
+    auto upload = [&](bool is_a, int idx) {
+        const int step = is_a ? step_m : step_n, rows = rows_of(idx, step, is_a ? m : n);
+        const size_t off = static_cast<size_t>(idx) * step * k;
+        if (k) keep(cudaMemcpyAsync((is_a ? da : dbw) + off, (is_a ? ha : hb) + off, static_cast<size_t>(rows) * k,
+                                    cudaMemcpyHostToDevice, ctx->copy_in));
+        keep(cudaEventRecord(is_a ? up_a[idx] : up_b[idx], ctx->copy_in));
+    };
+    auto block = [&](int i, int j, cudaEvent_t newest) {          // C block (i, j): operator, then its download
+        const int mi = rows_of(i, step_m, m), nj = rows_of(j, step_n, n);
+        const size_t c_off = static_cast<size_t>(i) * step_m * n + static_cast<size_t>(j) * step_n;
+        keep(cudaStreamWaitEvent(ctx->compute, newest, 0));       // copy_in is ordered: the newest upload implies the older ones
+        keep(gemm_dispatch(mi, k, nj, da + static_cast<size_t>(i) * step_m * k, a_dtype, k,
+                           db + static_cast<size_t>(j) * step_n * k, b_dtype, k, dc + c_off, n, &opt, ctx->compute));
+        cudaEvent_t d = done[i * bn + j];
+        keep(cudaEventRecord(d, ctx->compute));
+        keep(cudaStreamWaitEvent(ctx->copy_out, d, 0));
+        keep(cudaMemcpy2DAsync(c_host + c_off, static_cast<size_t>(n) * 4, dc + c_off, static_cast<size_t>(n) * 4,
+                               static_cast<size_t>(nj) * 4, mi, cudaMemcpyDeviceToHost, ctx->copy_out));
+    };
+    int na = 0, nb = 0;                                            // operand blocks uploaded so far
+    upload(true, na++);
+    upload(false, nb++);
+    block(0, 0, up_b[0]);
+    while ((na < bm || nb < bn) && first == cudaSuccess) {
+        if (nb < bn && (nb <= na || na == bm)) {                   // next block of B: a new block column of C
+            upload(false, nb);
+            for (int i = 0; i < na; ++i) block(i, nb, up_b[nb]);
+            ++nb;
+        } else {                                                   // next block of A: a new block row of C
+            upload(true, na);
+            for (int j = 0; j < nb; ++j) block(na, j, up_a[na]);
+            ++na;
         }
     }
     keep(cudaStreamSynchronize(ctx->copy_in));
     keep(cudaStreamSynchronize(ctx->compute));
     keep(cudaStreamSynchronize(ctx->copy_out));
-    for (int j = 0; j < blocks; ++j) { cudaEventDestroy(up[j]); cudaEventDestroy(done[j]); }
+    for (int i = 0; i < bm; ++i) cudaEventDestroy(up_a[i]);
+    for (int j = 0; j < bn; ++j) cudaEventDestroy(up_b[j]);
+    for (int t = 0; t < bm * bn; ++t) cudaEventDestroy(done[t]);
     return first;
 }
 

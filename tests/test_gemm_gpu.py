@@ -391,8 +391,11 @@ def test_config5_full_size_one_rank_shard(g, oracle):
 
 # ---------------------------------------------------------------- host-pointer entry point, generator, drop-in binary
 
-@pytest.mark.parametrize("shape", [(300, 272, 520), (64, 1024, 512), (2048, 2048, 4096), (8192, 4096, 4096), (4096, 4096, 8192)])
+@pytest.mark.parametrize("shape", [(300, 272, 520), (64, 1024, 512), (2048, 2048, 4096), (8192, 4096, 4096), (4096, 4096, 8192),
+                                   (4608, 2048, 12288), (5000, 3072, 9000), (12288, 1024, 12288)])
 def test_host_entry_point_matches_device_entry(g, oracle, shape):
+    """The host entry computes C as a grid of blocks (uploads, operator and downloads pipelined); every element still
+    sums its K products in the same order, so the result equals the one-call device result bit for bit."""
     m, k, n = shape
     a, b = random_operands(g, m, k, n, 0, 1, seed=23)
     dev_out = run(g, a, b, m, k, n)
