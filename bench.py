@@ -155,6 +155,32 @@ def cpu_reference_rate(M, K, N, rows_per_thread: int, seed_a: int, seed_b: int):
     return flops / dt / 1e12, threads, f"rows 0..{rows - 1} x cols 0..{cols - 1} of C at full K={K} ({flops / 1e9:.2f} GFLOP)", dt
 
 
+def reference_binary_rate(size: int = 512):
+    """The reference's OWN compiled CPU loop (its unmodified gemm_main.cpp built over host stand-ins, oracle/_ref):
+    wall time of a run with verify = 1 minus a run with verify = 0 at size^3 -- the difference is exactly its
+    single-threaded verification loop (GEMM/gemm_main.cpp:39-53).  None where the binary was not built."""
+    import subprocess
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_gemm_cpu")
+    if not os.path.exists(exe):
+        return None
+    def run(verify):
+        t0 = time.perf_counter()
+        subprocess.run([exe, str(size), str(size), str(size), "2", str(verify), "0", "0"], check=True,
+                       stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL, timeout=120)
+        return time.perf_counter() - t0
+    try:
+        base = min(run(0), run(0))
+        full = min(run(1), run(1))
+    except Exception:
+        return None
+    loop = full - base
+    if loop <= 0:
+        return None
+    return {"value": 2.0 * size ** 3 / loop / 1e12, "unit": "TFLOPS", "cores": 1, "kind": "reference",
+            "sample": f"{size}^3 e4m3 x e4m3, the reference driver's own verification loop, {loop:.2f} s "
+                      "(run with verify = 1 minus run with verify = 0)"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -184,6 +210,9 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    ref_loop = reference_binary_rate()
+    if ref_loop is not None:
+        line["cpu_baseline"]["reference_loop"] = ref_loop
     print(json.dumps(line))
     return 0
 
@@ -608,6 +637,9 @@ def main() -> int:
         line["cpu_baseline"] = {"value": r, "unit": "TFLOPS", "cores": threads, "kind": "port",
                                 "sample": sample + f", {dt:.1f} s; the reference's float loop "
                                 "(GEMM/gemm_main.cpp:45-52) restated in oracle/fp8_oracle.c, OpenMP over rows"}
+        ref_loop = reference_binary_rate()
+        if ref_loop is not None:                  # the reference's own binary, single thread as it ships
+            line["cpu_baseline"]["reference_loop"] = ref_loop
 
     if rank == 0:
         sys.stdout.flush()
