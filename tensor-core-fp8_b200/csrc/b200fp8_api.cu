@@ -303,8 +303,13 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         case B200FP8_KERNEL_PAIR_N512:
             return depth == 2 ? B200FP8_LAUNCH4(256, 2, 2, 2) : B200FP8_LAUNCH4(256, 4, 2, 2);
         case B200FP8_KERNEL_SKINNY: {
+            long long* trace = nullptr;
+            if (tune().debug & 1024) {                           // diagnostics: eight time stamps per CTA
+                if (!g_trace) { cudaMalloc(&g_trace, 3 * 4096 * sizeof(long long)); cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long)); }
+                if (static_cast<long long>((n + kSkinnyTileN - 1) / kSkinnyTileN) * 8 * 8 <= 3 * 4096) trace = g_trace;
+            }
             e = launch_skinny(ctx->sm_count, ctx->status, g_encode, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
-                              depth, split_k, epi, stream);
+                              depth, split_k, epi, stream, nullptr, 0, trace);
             if (e == cudaSuccess) ++t_launches;
             return e;
         }

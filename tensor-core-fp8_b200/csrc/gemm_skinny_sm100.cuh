@@ -44,6 +44,7 @@ struct SkinnyArgs {
     // col = ell_col_ind[nt * kb_total + kb]; col < 0 or beyond K is a padding block (zeros are loaded for both).
     const int* ell_col_ind;
     int ell_oob_a, ell_oob_b;   // 128-aligned k coordinates beyond A's K / beyond the compact B
+    long long* trace;    // diagnostics: eight globaltimer stamps per CTA (nullptr = off)
     Epilogue epi;        // extended epilogue (alpha, beta, scales, 16-bit output); inactive for the plain operator
 };
 
@@ -99,6 +100,8 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
 
+    long long* trace = args.trace ? args.trace + 8ll * (blockIdx.y * gridDim.x + blockIdx.x) : nullptr;
+    if (trace && threadIdx.x == 0) trace[0] = static_cast<long long>(ptx::globaltimer_ns());
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < stages; ++s) {
@@ -118,6 +121,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
+    if (trace && threadIdx.x == 0) trace[1] = static_cast<long long>(ptx::globaltimer_ns());
 
     float epi_alpha = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
     if (args.epi.active) {
@@ -191,6 +195,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                 break;
             }
             ptx::tc_fence_after();
+            if (trace && kb == kb0 && lane == 0) trace[2] = static_cast<long long>(ptx::globaltimer_ns());
             const uint32_t b_src = smem_base + s * L::kStageBytes;
             const uint64_t adesc = ptx::umma_desc_k128(b_src);                 // 128 rows of B
             const uint64_t bdesc = ptx::umma_desc_k128(b_src + L::kBBytes);    // MP rows of A
@@ -205,6 +210,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         }
         if (ok && ptx::elect_one()) ptx::umma_commit(bar_acc);
         __syncwarp();
+        if (trace && lane == 0) trace[3] = static_cast<long long>(ptx::globaltimer_ns());
     } else {
         // ---------------- epilogue: 128 threads, thread = one column n of C ----------------
         // bar_acc completes after every MMA of this CTA has finished, i.e. after the ring's
@@ -214,6 +220,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         const int n = n0 + n_local;
         bool ok = wait_bounded(bar_acc, 0, abort_flag, false);
         if (!ok) record_failure(args.status, abort_flag, kStatusSkinnyTimeout);
+        if (trace && warp == 2 && lane == 0) trace[4] = static_cast<long long>(ptx::globaltimer_ns());
         __syncwarp();
         ptx::tc_fence_after();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -245,6 +252,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         // ---------------- reduce-scatter across the cluster through distributed shared memory ----------------
         ptx::cluster_arrive();
         ptx::cluster_wait();
+        if (trace && threadIdx.x == 0) trace[5] = static_cast<long long>(ptx::globaltimer_ns());
         const int rows_per = (args.M + args.splits - 1) / args.splits;
         const int m_begin = split * rows_per;
         const int m_end = min(args.M, m_begin + rows_per);
@@ -280,6 +288,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                 }
             }
         }
+        if (trace && threadIdx.x == 0) trace[6] = static_cast<long long>(ptx::globaltimer_ns());
         // peers may still be reading this CTA's shared memory
         ptx::cluster_arrive();
         ptx::cluster_wait();
@@ -289,6 +298,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
 
     ptx::tc_fence_before();
     __syncthreads();
+    if (trace && threadIdx.x == 0) trace[7] = static_cast<long long>(ptx::globaltimer_ns());
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem_base, L::kTmemCols);
@@ -369,7 +379,7 @@ cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const
 inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, int m, int k, int n, const void* a,
                                  long long lda, const void* b, long long ldb, float* c, long long ldc, int a_dtype,
                                  int b_dtype, int depth, int split_k, const Epilogue* epi, cudaStream_t stream,
-                                 const int* ell_col_ind = nullptr, int ell_k_small = 0) {
+                                 const int* ell_col_ind = nullptr, int ell_k_small = 0, long long* trace = nullptr) {
     // With ell_col_ind the large operand B is in blocked-ELL form: `k` is the width of its compact values matrix
     // (blocks per row x 128) and ell_k_small the K of the small operand A.
     const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
@@ -384,6 +394,7 @@ inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, 
     args.C = c; args.ldc = ldc;
     args.status = status;
     if (epi) args.epi = *epi;
+    args.trace = trace;
     if (ell_col_ind) {
         args.ell_col_ind = ell_col_ind;
         args.ell_oob_a = (ell_k_small + kBlockK - 1) / kBlockK * kBlockK;
