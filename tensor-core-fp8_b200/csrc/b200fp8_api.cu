@@ -757,6 +757,17 @@ long long b200fp8_launch_count(void) { return t_launches; }
 // diagnostics: device pointer of the k-block timestamp trace (B200FP8_DEBUG & 64), or NULL
 void* b200fp8_debug_trace(void) { return g_trace; }
 
+// diagnostics: copies the first `count` trace words to the host (after a device synchronise) and, with
+// `clear`, zeroes the device buffer for the next launch.  Returns the number of words copied (0: no trace).
+int b200fp8_debug_trace_copy(long long* dst, int count, int clear) {
+    if (!g_trace || !dst || count <= 0) return 0;
+    if (count > 3 * 4096) count = 3 * 4096;
+    if (cudaDeviceSynchronize() != cudaSuccess) return 0;
+    if (cudaMemcpy(dst, g_trace, static_cast<size_t>(count) * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    if (clear) cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long));
+    return count;
+}
+
 const char* b200fp8_version(void) { return "b200fp8 0.1 sm_100a"; }
 
 }  // extern "C"
