@@ -16,6 +16,7 @@
 // Same operator contract as the main kernel (reference: gemm::GEMM, GEMM/include/gemm.cuh:12-55;
 // the reference's kernels write nothing at all for M < 128, GEMM/src/gemm.cu:45-47).
 #pragma once
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
@@ -328,7 +329,12 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
     const int kb_total = (k + kBlockK - 1) / kBlockK;
     int s = split_k;
     if (s <= 0) {
-        s = (2 * sm_count) / n_tiles;
+        // CTAs per SM aimed at: two for small M; one for M > 32, where half as many splits halve the reduce-scatter
+        // and a single CTA can afford a ring twice as deep (B200FP8_SKINNY_CTAS_PER_SM overrides)
+        static const int fill_env = [] { const char* v = getenv("B200FP8_SKINNY_CTAS_PER_SM"); return v ? atoi(v) : 0; }();
+        const int fill = fill_env > 0 ? fill_env : (mp >= 64 ? 1 : 2);
+        s = (fill * sm_count) / n_tiles;
+        if (s < 1) s = (2 * sm_count) / n_tiles;
         if (s < 1) s = 1;
     }
     if (s > kSkinnyMaxSplits) s = kSkinnyMaxSplits;
@@ -340,7 +346,9 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
     int st = depth;
     if (st <= 0) {
         const int stage_bytes = (kSkinnyTileN + mp) * kBlockK;
-        st = (108 * 1024) / stage_bytes;     // two CTAs per SM
+        // two CTAs per SM share its shared memory; a grid that fits one CTA per SM gets all of it
+        const int budget = (static_cast<long long>(n_tiles) * s <= sm_count ? 216 : 108) * 1024;
+        st = budget / stage_bytes;
         if (st > 8) st = 8;
         if (st < 2) st = 2;
     }
