@@ -574,7 +574,9 @@ def main() -> int:
             cmp.b200fp8_cmp_cublaslt.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci, fp, ctypes.POINTER(ci), vp]
             cmp.b200fp8_cmp_cublaslt_run.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, fp, vp]
         stream = torch.cuda.current_stream().cuda_stream
-        for name in ("gemm8192", args.workload):
+        # a short workload goes first: after the power-capped 8192^3 runs the clocks need a while to recover
+        order = (args.workload, "gemm8192") if 2.0 * M * K * n_local < 2e12 else ("gemm8192", args.workload)
+        for name in order:
             if name in extras:
                 continue
             m2, k2, n2, _ = WORKLOADS[name]
@@ -599,15 +601,26 @@ def main() -> int:
                                                     ctypes.byref(ms), ctypes.byref(found), stream) == 0
             ours, theirs = [], []
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            side_graph = None
-            if fl < 2e12:                                 # same launch-overhead treatment as the main loop
-                for _ in range(2):
-                    g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+            # short kernels: both sides as CUDA graphs of `iters` launches (no launch gaps on either side) over the
+            # workload's rotating operand sets (every launch streams from HBM); long ones launch by launch
+            side_graph = their_graph = None
+            rot_b, rot_c = (bs, cs) if name == args.workload else ([b2], [c2])
+            if fl < 2e12:
+                for i in range(2):
+                    g.gemm_ex(a2, rot_b[i % len(rot_b)], rot_c[i % len(rot_c)], depth=args.depth, kernel=args.kernel)
                 torch.cuda.synchronize()
                 side_graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(side_graph):
-                    for _ in range(iters):
-                        g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
+                    for i in range(iters):
+                        g.gemm_ex(a2, rot_b[i % len(rot_b)], rot_c[i % len(rot_c)], depth=args.depth, kernel=args.kernel)
+                if have_cmp:
+                    cmp.b200fp8_cmp_cublaslt_enqueue.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp]
+                    their_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(their_graph):
+                        cap = torch.cuda.current_stream().cuda_stream
+                        for i in range(iters):
+                            cmp.b200fp8_cmp_cublaslt_enqueue(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), rot_b[i % len(rot_b)].data_ptr(),
+                                                             g.dtype_code(b2), rot_c[i % len(rot_c)].data_ptr(), cap)
 
             def ours_launches(count):
                 if side_graph is not None:
@@ -624,7 +637,15 @@ def main() -> int:
                 torch.cuda.synchronize()
                 if rnd:                                   # the first pass warms both up
                     ours.append(e0.elapsed_time(e1) / iters)
-                if have_cmp:
+                if their_graph is not None:
+                    their_graph.replay()
+                    e0.record()
+                    their_graph.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if rnd:
+                        theirs.append(e0.elapsed_time(e1) / iters)
+                elif have_cmp:
                     ms = ctypes.c_float(-1)
                     cmp.b200fp8_cmp_cublaslt_run(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), b2.data_ptr(), g.dtype_code(b2), c2.data_ptr(), lead,
                                                  ctypes.byref(ms), stream)
@@ -634,7 +655,9 @@ def main() -> int:
                         theirs.append(ms.value)
             o = sum(ours) / len(ours)
             entry = {"ms": o, "tflops": fl / o / 1e9,
-                     "protocol": f"3 alternating rounds, each {lead} untimed lead-in launches then {iters} timed"}
+                     "protocol": f"3 alternating rounds, each {lead} untimed lead-in launches then {iters} timed"
+                                 + ("; both sides as CUDA graphs" + (f" over {len(rot_b)} rotating operand sets" if len(rot_b) > 1 else "")
+                                    if side_graph is not None else "")}
             if theirs:
                 t_ = sum(theirs) / len(theirs)
                 entry.update({"cublaslt_ms": t_, "cublaslt_tflops": fl / t_ / 1e9, "vs_cublaslt": t_ / o})
