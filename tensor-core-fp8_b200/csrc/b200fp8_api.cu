@@ -107,9 +107,11 @@ struct Tune {
     int pace_limit_ns = 30000;
     int store_gap_ns = 0;
     int split_tail = 1;
+    int pdl = 1;                  // launch with programmatic stream serialization (set-up overlaps the previous kernel's tail)
     int host_block_m = 4096;      // host-pointer entry: edge of the C blocks it pipelines over (rows / columns)
     int host_block_n = 4096;
     Tune() {
+        if (const char* v = getenv("B200FP8_PDL")) pdl = atoi(v);
         if (const char* v = getenv("B200FP8_HOST_BLOCK_M")) host_block_m = atoi(v) >= 256 ? atoi(v) : host_block_m;
         if (const char* v = getenv("B200FP8_HOST_BLOCK_N")) host_block_n = atoi(v) >= 256 ? atoi(v) : host_block_n;
         if (const char* v = getenv("B200FP8_SPLIT_TAIL")) split_tail = atoi(v);
@@ -232,11 +234,13 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
     cfg.dynamicSmemBytes = L::kDynamicBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddep_wait in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tune().pdl ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, tbh, args);
     if (e == cudaSuccess) ++t_launches;
     return e;
@@ -309,7 +313,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
                 if (static_cast<long long>((n + kSkinnyTileN - 1) / kSkinnyTileN) * 8 * 8 <= 3 * 4096) trace = g_trace;
             }
             e = launch_skinny(ctx->sm_count, ctx->status, g_encode, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
-                              depth, split_k, epi, stream, nullptr, 0, trace);
+                              depth, split_k, epi, stream, nullptr, 0, trace, tune().pdl);
             if (e == cudaSuccess) ++t_launches;
             return e;
         }
@@ -435,7 +439,7 @@ int b200fp8_spmv_bell_f32(int m, int k, const void* ell_values, int a_dtype, lon
     cudaError_t e = get_ctx(&ctx);
     if (e != cudaSuccess) return e;
     e = launch_skinny(ctx->sm_count, ctx->status, g_encode, 1, static_cast<int>(width), m, x, k, ell_values, lda, y, m,
-                      x_dtype, a_dtype, depth, split_k, nullptr, st, ell_col_ind, k);
+                      x_dtype, a_dtype, depth, split_k, nullptr, st, ell_col_ind, k, nullptr, tune().pdl);
     if (e == cudaSuccess) ++t_launches;
     return e;
 }

@@ -46,6 +46,7 @@ struct SkinnyArgs {
     const int* ell_col_ind;
     int ell_oob_a, ell_oob_b;   // 128-aligned k coordinates beyond A's K / beyond the compact B
     long long* trace;    // diagnostics: eight globaltimer stamps per CTA (nullptr = off)
+    int pdl;             // host only: launch with programmatic stream serialization
     Epilogue epi;        // extended epilogue (alpha, beta, scales, 16-bit output); inactive for the plain operator
 };
 
@@ -122,6 +123,10 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
+    // Everything above touched only this CTA's own resources and may overlap the previous kernel's tail;
+    // global memory (operands, C, the status word) is touched only after the grids before this one are complete.
+    ptx::griddep_wait();
+    ptx::griddep_launch_dependents();
     if (trace && threadIdx.x == 0) trace[1] = static_cast<long long>(ptx::globaltimer_ns());
 
     float epi_alpha = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
@@ -374,20 +379,22 @@ cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const
     cfg.blockDim = dim3(kSkinnyThreads, 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(bytes);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = static_cast<unsigned>(args.splits);
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see griddep_wait in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = args.pdl ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, tb, ta, args);
 }
 
 inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, int m, int k, int n, const void* a,
                                  long long lda, const void* b, long long ldb, float* c, long long ldc, int a_dtype,
                                  int b_dtype, int depth, int split_k, const Epilogue* epi, cudaStream_t stream,
-                                 const int* ell_col_ind = nullptr, int ell_k_small = 0, long long* trace = nullptr) {
+                                 const int* ell_col_ind = nullptr, int ell_k_small = 0, long long* trace = nullptr, int pdl = 0) {
     // With ell_col_ind the large operand B is in blocked-ELL form: `k` is the width of its compact values matrix
     // (blocks per row x 128) and ell_k_small the K of the small operand A.
     const int mp = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
@@ -403,6 +410,7 @@ inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, 
     args.status = status;
     if (epi) args.epi = *epi;
     args.trace = trace;
+    args.pdl = pdl;
     if (ell_col_ind) {
         args.ell_col_ind = ell_col_ind;
         args.ell_oob_a = (ell_k_small + kBlockK - 1) / kBlockK * kBlockK;

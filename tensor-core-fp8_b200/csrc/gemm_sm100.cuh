@@ -270,6 +270,11 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (pair) { ptx::cluster_arrive(); ptx::cluster_wait(); }
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
+    // Everything above touched only this CTA's own resources and may overlap the previous kernel's tail;
+    // global memory (operands, C, pacing counter, status word) is touched only after the grids before this one are
+    // complete.  The next kernel of the stream may be set up while this one runs; its own wait holds it back.
+    ptx::griddep_wait();
+    ptx::griddep_launch_dependents();
 
     // persistent walk over work items, identical in every role
     const int num_items = args.full_items + 2 * args.split_tiles;

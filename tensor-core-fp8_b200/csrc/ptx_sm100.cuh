@@ -48,6 +48,12 @@ __device__ __forceinline__ void cluster_wait() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// Programmatic dependent launch.  wait: returns once every grid this one depends on has completed and its
+// memory is visible (immediately when the launch carried no programmatic dependency).  launch_dependents: lets
+// the next kernel of the stream be set up while this one runs; its own wait still holds it until this grid is done.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
