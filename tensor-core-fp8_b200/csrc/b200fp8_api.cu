@@ -77,9 +77,25 @@ cudaError_t get_ctx(DeviceCtx** out) {
 }
 
 // 2-D tensor map over a row-major matrix of `rows` x `cols` elements with row pitch `ld` elements.
+// A descriptor is a pure function of these arguments, so each host thread keeps the last few it encoded: a caller
+// that repeats a call with the same pointers (a benchmark loop, a layer called every step) skips the encoding.
 cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t cols,
                       uint64_t rows, uint64_t ld, uint32_t box_cols, uint32_t box_rows,
                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+    struct Key {
+        const void* base; uint64_t cols, rows, ld; uint32_t box_cols, box_rows; int type, elem_bytes, swizzle;
+        bool operator==(const Key& o) const {
+            return base == o.base && cols == o.cols && rows == o.rows && ld == o.ld && box_cols == o.box_cols &&
+                   box_rows == o.box_rows && type == o.type && elem_bytes == o.elem_bytes && swizzle == o.swizzle;
+        }
+    };
+    constexpr int kSlots = 16;
+    struct Cache { Key key[kSlots]; CUtensorMap map[kSlots]; bool used[kSlots]; };
+    static thread_local Cache cache = {};
+    const Key key{base, cols, rows, ld, box_cols, box_rows, static_cast<int>(type), elem_bytes, static_cast<int>(swizzle)};
+    const uint64_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull + cols * 31 + rows * 131 + box_rows * 7 + box_cols;
+    const int slot = static_cast<int>((h >> 32) % kSlots);
+    if (cache.used[slot] && cache.key[slot] == key) { *map = cache.map[slot]; return cudaSuccess; }
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
     const cuuint32_t box[2] = {box_cols, box_rows};
@@ -87,7 +103,9 @@ cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes
     CUresult r = g_encode(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    cache.key[slot] = key; cache.map[slot] = *map; cache.used[slot] = true;
+    return cudaSuccess;
 }
 
 // Destinations of the fused all-gather epilogue: this rank's column block inside every peer's C.
