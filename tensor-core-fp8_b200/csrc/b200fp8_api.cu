@@ -305,6 +305,9 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // long runs are power-limited: the wide tile moves a quarter less data per flop
         else if (wide_tiles >= 16LL * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N512;
         else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
+        // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
+        // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
+        else if (4 * pair_tiles >= 3 * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N256;
         else if (n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
