@@ -298,19 +298,23 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
             }
         }
         if (trace && threadIdx.x == 0) trace[6] = static_cast<long long>(ptx::globaltimer_ns());
-        // peers may still be reading this CTA's shared memory
-        if (clustered) { ptx::cluster_arrive(); ptx::cluster_wait(); }
+        // Peers may still be reading this CTA's shared memory: it must not exit before all of them have arrived
+        // here too.  The wait for that comes last, so that the rest of the teardown overlaps the barrier's latency.
+        __syncwarp();
+        if (clustered) ptx::cluster_arrive();
     }
     __syncwarp();
     if (args.epi.amax != nullptr) amax_merge_warp(args.epi.amax, epi_amax);
 
     ptx::tc_fence_before();
     __syncthreads();
-    if (trace && threadIdx.x == 0) trace[7] = static_cast<long long>(ptx::globaltimer_ns());
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem_base, L::kTmemCols);
     }
+    __syncwarp();
+    if (clustered) ptx::cluster_wait();
+    if (trace && threadIdx.x == 0) trace[7] = static_cast<long long>(ptx::globaltimer_ns());
 }
 
 using SkinnyEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
