@@ -389,6 +389,33 @@ def test_config5_full_size_one_rank_shard(g, oracle):
     assert freivalds(a, b, out) <= 1.0
 
 
+# ---------------------------------------------------------------- size-independent properties at large sizes
+
+@pytest.mark.parametrize("shape", [(2048, 4096, 3072), (8192, 8192, 4096), (4096, 2048, 8192)])
+@pytest.mark.parametrize("fa,fb", [(0, 0), (0, 1)])
+def test_transpose_symmetry_is_bitwise(g, shape, fa, fb):
+    """(A B^T)^T = B A^T: every product a*b is the same number either way round and each element sums its K products
+    in the same order (k-blocks in sequence), whatever tile or kernel the swapped shape selects: identical bits."""
+    m, k, n = shape
+    a, b = random_operands(g, m, k, n, fa, fb, seed=31)
+    c = run(g, a, b, m, k, n)
+    ct = run(g, b, a, n, k, m)
+    assert torch.equal(c, ct.T)
+
+
+def test_row_permutation_and_row_blocks_are_bitwise(g):
+    """Rows of C depend only on their own row of A: permuting A's rows permutes C's rows, and any row block computed
+    alone (other tile shapes, other kernels) equals the same rows of the full result."""
+    m, k, n = 4096, 4096, 4096
+    a, b = random_operands(g, m, k, n, 0, 0, seed=33)
+    c = run(g, a, b, m, k, n)
+    perm = torch.randperm(m, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    ap = a.view(torch.uint8)[perm].contiguous().view(a.dtype)
+    assert torch.equal(run(g, ap, b, m, k, n), c[perm])
+    for r0, r1 in ((0, 300), (1000, 1257), (4096 - 640, 4096)):          # 300 and 257 rows pick other kernels than 4096
+        assert torch.equal(run(g, a[r0:r1], b, r1 - r0, k, n), c[r0:r1])
+
+
 # ---------------------------------------------------------------- host-pointer entry point, generator, drop-in binary
 
 @pytest.mark.parametrize("shape", [(300, 272, 520), (64, 1024, 512), (2048, 2048, 4096), (8192, 4096, 4096), (4096, 4096, 8192),
