@@ -670,7 +670,8 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (args.store_gap_ns && c + 2 < chunks) __nanosleep(args.store_gap_ns);
             }
         }
-        if (issuer) ptx::bulk_wait_group<0>();                    // all stores of this warp are complete
+        // the staging box must outlive the stores' reads of it; the writes themselves complete with the grid
+        if (issuer) ptx::bulk_wait_group_read<0>();
         __syncwarp();
         if (args.epi.amax != nullptr) amax_merge_warp(args.epi.amax, epi_amax);
     }
