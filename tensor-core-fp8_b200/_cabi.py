@@ -18,6 +18,7 @@ KERNEL_CTA1_N128 = 2
 KERNEL_PAIR_N256 = 3
 KERNEL_SKINNY = 4
 KERNEL_PAIR_N512 = 5
+KERNEL_PAIR_N128 = 6
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libb200fp8.so")

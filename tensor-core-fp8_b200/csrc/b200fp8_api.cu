@@ -289,7 +289,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     const int split_k = opt ? opt->split_k : 0;
     const int max_ctas = opt ? opt->max_ctas : 0;
     if (depth != 0 && depth != 2 && depth != 4) return cudaErrorInvalidValue;
-    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_PAIR_N512) return cudaErrorInvalidValue;
+    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_PAIR_N128) return cudaErrorInvalidValue;
     if (split_k < 0 || max_ctas < 0) return cudaErrorInvalidValue;
 
     DeviceCtx* ctx = nullptr;
@@ -300,6 +300,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
         const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
         const long long wide_tiles = static_cast<long long>((m + 255) / 256) * ((n + 511) / 512);
+        const long long n128_cols = (n + 127) / 128;
         if (ell) kernel = n256_tiles >= ctx->sm_count / 2 ? B200FP8_KERNEL_CTA1_N256 : B200FP8_KERNEL_CTA1_N128;
         else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
         // long runs are power-limited: the wide tile moves a quarter less data per flop
@@ -308,6 +309,10 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
         // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
         else if (4 * pair_tiles >= 3 * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N256;
+        // one row of 256 x 128 pair tiles that fills most of the pairs: a quarter less operand traffic per CTA than
+        // 128 x 128 tiles (measured at M = 130..256, N = K = 8192: 5-7 %)
+        else if (m <= 256 && k >= 8192 && 4 * n128_cols >= 3 * (ctx->sm_count / 2) && n128_cols <= ctx->sm_count / 2)
+            kernel = B200FP8_KERNEL_PAIR_N128;
         else if (n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
@@ -325,6 +330,8 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
             return depth == 2 ? B200FP8_LAUNCH(128, 2, 1) : depth == 4 ? B200FP8_LAUNCH(128, 4, 1) : B200FP8_LAUNCH(128, 6, 1);
         case B200FP8_KERNEL_PAIR_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 2) : depth == 4 ? B200FP8_LAUNCH(256, 4, 2) : B200FP8_LAUNCH(256, 6, 2);
+        case B200FP8_KERNEL_PAIR_N128:
+            return depth == 2 ? B200FP8_LAUNCH(128, 2, 2) : depth == 4 ? B200FP8_LAUNCH(128, 4, 2) : B200FP8_LAUNCH(128, 8, 2);
         case B200FP8_KERNEL_PAIR_N512:
             return depth == 2 ? B200FP8_LAUNCH4(256, 2, 2, 2) : B200FP8_LAUNCH4(256, 4, 2, 2);
         case B200FP8_KERNEL_SKINNY: {
