@@ -125,11 +125,14 @@ struct Tune {
     int pace_limit_ns = 30000;
     int store_gap_ns = 0;
     int split_tail = 1;
+    int l2_loads = 0, l2_stores = 0;   // L2 eviction hints of operand loads / C stores (see GemmArgs)
     int pdl = 1;                  // launch with programmatic stream serialization (set-up overlaps the previous kernel's tail)
     int host_block_m = 4096;      // host-pointer entry: edge of the C blocks it pipelines over (rows / columns)
     int host_block_n = 4096;
     Tune() {
         if (const char* v = getenv("B200FP8_PDL")) pdl = atoi(v);
+        if (const char* v = getenv("B200FP8_L2_LOADS")) l2_loads = atoi(v);
+        if (const char* v = getenv("B200FP8_L2_STORES")) l2_stores = atoi(v);
         if (const char* v = getenv("B200FP8_HOST_BLOCK_M")) host_block_m = atoi(v) >= 256 ? atoi(v) : host_block_m;
         if (const char* v = getenv("B200FP8_HOST_BLOCK_N")) host_block_n = atoi(v) >= 256 ? atoi(v) : host_block_n;
         if (const char* v = getenv("B200FP8_SPLIT_TAIL")) split_tail = atoi(v);
@@ -178,6 +181,8 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     args.n_tiles = (n + L::kTileN - 1) / L::kTileN;
     args.group_m = (CTAS == 2) ? tune().group_m_pair : tune().group_m_single;
     args.wait_hint_ns = static_cast<uint32_t>(tune().wait_hint_ns);
+    args.l2_loads = tune().l2_loads;
+    args.l2_stores = tune().l2_stores;
     args.debug = tune().debug;
     args.store_gap_ns = (NACC == 1) ? static_cast<unsigned int>(tune().store_gap_ns) : 0u;
     if (args.debug & (64 | 128)) {

@@ -119,6 +119,8 @@ struct GemmArgs {
     int full_items;       // number of full-width work items (= tiles - split_tiles)
     int split_tiles;      // tiles handled as two halves each (0 = off)
     uint32_t idesc_half;  // instruction descriptor for N = BN / 2
+    int l2_loads;         // L2 eviction hint of the operand loads: 0 none, 1 evict_last, 2 evict_first
+    int l2_stores;        // ... of the FP32 TMA stores of C: 0 none, 2 evict_first
     int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
     uint32_t wait_hint_ns; // suspend-time hint for long mbarrier waits (0 = plain polling)
     int debug;            // diagnostics only (results become wrong): 1 skip TMA loads, 2 skip C stores, 4 skip MMAs,
@@ -309,6 +311,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (warp == 0) {
         // ---------------- TMA producer: warp-uniform loop, one elected lane issues ----------------
         const uint32_t full0 = pair ? ptx::mapa(bar_full, 0) : bar_full;   // the leader's full barriers
+        const uint64_t load_policy = ptx::l2_policy(args.l2_loads);
         int s = 0;
         uint32_t ph = 0;
         int issued = 0;
@@ -368,16 +371,30 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
                     } else if (pair) {
                         if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
-                        ptx::tma_load_2d_pair(a_dst, &tmap_a, ka, m0, full0 + 8 * s);
+                        if (args.l2_loads) {
+                            ptx::tma_load_2d_pair_hint(a_dst, &tmap_a, ka, m0, full0 + 8 * s, load_policy);
 #pragma unroll
-                        for (int j = 0; j < NACC; ++j)
-                            ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, full0 + 8 * s);
+                            for (int j = 0; j < NACC; ++j)
+                                ptx::tma_load_2d_pair_hint(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, full0 + 8 * s, load_policy);
+                        } else {
+                            ptx::tma_load_2d_pair(a_dst, &tmap_a, ka, m0, full0 + 8 * s);
+#pragma unroll
+                            for (int j = 0; j < NACC; ++j)
+                                ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, full0 + 8 * s);
+                        }
                     } else {
                         ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
-                        ptx::tma_load_2d(a_dst, &tmap_a, ka, m0, bar_full + 8 * s);
+                        if (args.l2_loads) {
+                            ptx::tma_load_2d_hint(a_dst, &tmap_a, ka, m0, bar_full + 8 * s, load_policy);
 #pragma unroll
-                        for (int j = 0; j < NACC; ++j)
-                            ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, bar_full + 8 * s);
+                            for (int j = 0; j < NACC; ++j)
+                                ptx::tma_load_2d_hint(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, bar_full + 8 * s, load_policy);
+                        } else {
+                            ptx::tma_load_2d(a_dst, &tmap_a, ka, m0, bar_full + 8 * s);
+#pragma unroll
+                            for (int j = 0; j < NACC; ++j)
+                                ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, bar_full + 8 * s);
+                        }
                     }
                 }
                 __syncwarp();
@@ -477,6 +494,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t sb = smem_base + L::kEpiOff + (warp - 2) * L::kEpiBufBytes;   // this warp's staging box
         const uint32_t tempty0 = pair ? ptx::mapa(bar_tempty, 0) : bar_tempty;
         const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
+        const uint64_t store_policy = ptx::l2_policy(args.l2_stores);
         constexpr int kChunks = BN / 32 / (NACC == 1 ? 2 : 1);    // 32-column chunks this warp drains per tile
         float epi_alpha = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
         if (args.epi.active) {
@@ -587,8 +605,10 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (issuer) {
-                        if (row0 < args.M && col0 < args.N && !(args.debug & 2) && args.mc_c == nullptr)
-                            ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        if (row0 < args.M && col0 < args.N && !(args.debug & 2) && args.mc_c == nullptr) {
+                            if (args.l2_stores) ptx::tma_store_2d_hint(&tmap_c, sb, col0, row0, store_policy);
+                            else ptx::tma_store_2d(&tmap_c, sb, col0, row0);
+                        }
                         ptx::bulk_commit_group();
                     }
                     if (args.num_peers > 0 || args.mc_c != nullptr) {
