@@ -31,6 +31,10 @@
 // BF16/FP16 output) and, for N-sharded multi-GPU runs, the fused all-gather (finished boxes are
 // also stored into every peer's C, by unicast stores or one multimem store).
 //
+// Also: a blocked-ELL sparse A for the one-CTA variants (one table lookup per k-block in the producer), a
+// plain-store epilogue for C matrices TMA cannot write (transposed through the staging box: coalesced rows), and
+// programmatic dependent launch (set-up before griddepcontrol.wait, global memory only after it).
+//
 // Every wait on an mbarrier is bounded: after about two seconds the waiting warp records a
 // code in the device status word, raises a CTA-wide abort flag and leaves its loop, so a
 // broken pipeline ends the kernel instead of hanging the GPU.
