@@ -46,7 +46,8 @@ enum {
     B200FP8_KERNEL_PAIR_N256 = 3, /* CTA pair (cta_group::2) per 256x256 tile       */
     B200FP8_KERNEL_SKINNY = 4,    /* swap-AB split-K kernel for M <= 128 (HBM-bound) */
     B200FP8_KERNEL_PAIR_N512 = 5, /* CTA pair per 256x512 tile: least traffic per flop */
-    B200FP8_KERNEL_PAIR_N128 = 6  /* CTA pair per 256x128 tile: 128 < M <= 256 with a large N */
+    B200FP8_KERNEL_PAIR_N128 = 6, /* CTA pair per 256x128 tile: 128 < M <= 256 with a large N */
+    B200FP8_KERNEL_CTA1_N64 = 7   /* one CTA per 128x64 tile: twice the CTAs for problems of a few tiles */
 };
 
 typedef struct b200fp8_options {

@@ -19,6 +19,7 @@ KERNEL_PAIR_N256 = 3
 KERNEL_SKINNY = 4
 KERNEL_PAIR_N512 = 5
 KERNEL_PAIR_N128 = 6
+KERNEL_CTA1_N64 = 7
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libb200fp8.so")

@@ -679,6 +679,12 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // two register sets: the TMEM load of chunk c+1 is in flight while chunk c is stored
             uint32_t va[32], vb[32];
             ptx::tmem_ld_32x32(t_addr, va);
+            if constexpr (kChunks == 1) {                         // 64-column tile: one chunk per warp
+                ptx::tmem_ld_wait();
+                scale(va, 0);
+                release_slot();
+                emit(va, 0);
+            } else
 #pragma unroll 1
             for (int c = 0; c < chunks; c += 2) {
                 ptx::tmem_ld_wait();                              // va = chunk c

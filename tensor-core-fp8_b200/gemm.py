@@ -19,7 +19,7 @@ import torch
 
 from . import _cabi
 from ._cabi import (E4M3, E5M2, KERNEL_AUTO, KERNEL_CTA1_N128, KERNEL_CTA1_N256, KERNEL_PAIR_N256,  # noqa: F401
-                    KERNEL_PAIR_N128, KERNEL_PAIR_N512, KERNEL_SKINNY, B200Fp8Error, Options)
+                    KERNEL_CTA1_N64, KERNEL_PAIR_N128, KERNEL_PAIR_N512, KERNEL_SKINNY, B200Fp8Error, Options)
 
 _DTYPES = {torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
 

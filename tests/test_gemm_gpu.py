@@ -88,7 +88,7 @@ def test_golden_fixture_through_reference_api(g, oracle, path, entry):
 
 # ---------------------------------------------------------------- exact known answers
 
-@pytest.mark.parametrize("kernel", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("kernel", [1, 2, 3, 4, 5, 6, 7])
 @pytest.mark.parametrize("fa,fb", COMBOS)
 def test_one_hot_rows_select_columns_exactly(g, oracle, kernel, fa, fb):
     m, k, n = (64, 256, 384) if kernel == 4 else (384, 256, 640)
@@ -103,7 +103,7 @@ def test_one_hot_rows_select_columns_exactly(g, oracle, kernel, fa, fb):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6])
+@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6, 7])
 def test_powers_of_two_sum_exactly(g, oracle, kernel):
     m, k, n = (128, 512, 256) if kernel == 4 else (256, 512, 512)
     rng = np.random.default_rng(5)
@@ -136,6 +136,7 @@ def test_special_values_propagate(g, oracle):
     (5, 2, (512, 400, 1024)), (5, 4, (300, 208, 1030)), (5, 0, (1030, 1024, 1540)),
     (4, 0, (16, 1024, 1000)), (4, 2, (100, 2048, 384)), (4, 4, (128, 528, 260)),
     (6, 2, (256, 400, 512)), (6, 4, (200, 208, 516)), (6, 0, (700, 1024, 900)),
+    (7, 2, (256, 400, 512)), (7, 4, (200, 208, 516)), (7, 0, (700, 1024, 900)),
     (0, 0, (640, 256, 896)),
 ])
 def test_random_operands_all_kernels(g, oracle, fa, fb, kernel, depth, shape):
@@ -171,7 +172,7 @@ def test_ragged_m(g, oracle, m):
 
 
 @pytest.mark.parametrize("k", [16, 32, 48, 64, 112, 128, 144, 256, 4096 + 16])
-@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6])
+@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6, 7])
 def test_k_sweep_including_tails(g, oracle, k, kernel):
     m, n = (48, 200) if kernel == 4 else (260, 520)
     a, b = random_operands(g, m, k, n, 0, 1, seed=k)
