@@ -347,9 +347,9 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
         s = (fill * sm_count) / n_tiles;
         if (s < 1) s = (2 * sm_count) / n_tiles;
         if (s < 1) s = 1;
-        // clusters of 8 CTAs that each fill an SM only fit two to a GPC: with more than 8 of them some wait for a
-        // second round (M = 128, K = 8192, N = 2048: 17 us with 8 splits, 10.8 us with 4)
-        if (mp >= 64 && s > 4 && n_tiles > 8) s = 4;
+        // clusters of 8 CTAs pack badly into the GPCs: with more than 8 of them some wait for a second round
+        // (K = 8192, N = 2048: M = 128 17 us with 8 splits, 10.8 us with 4; M = 16 11.8 us against 7.6 us)
+        if (s > 4 && n_tiles > 8) s = 4;
     }
     if (s > kSkinnyMaxSplits) s = kSkinnyMaxSplits;
     if (s > kb_total) s = kb_total;
