@@ -44,17 +44,21 @@ enum {
     B200FP8_KERNEL_CTA1_N256 = 1, /* one CTA per 128x256 tile                       */
     B200FP8_KERNEL_CTA1_N128 = 2, /* one CTA per 128x128 tile                       */
     B200FP8_KERNEL_PAIR_N256 = 3, /* CTA pair (cta_group::2) per 256x256 tile       */
-    B200FP8_KERNEL_SKINNY = 4,    /* swap-AB split-K kernel for M <= 128 (HBM-bound) */
+    B200FP8_KERNEL_SKINNY = 4,    /* swap-AB split-K kernel for M <= 128, K splits of a tile in one cluster */
     B200FP8_KERNEL_PAIR_N512 = 5, /* CTA pair per 256x512 tile: least traffic per flop */
     B200FP8_KERNEL_PAIR_N128 = 6, /* CTA pair per 256x128 tile: 128 < M <= 256 with a large N */
-    B200FP8_KERNEL_CTA1_N64 = 7   /* one CTA per 128x64 tile: twice the CTAs for problems of a few tiles */
+    B200FP8_KERNEL_CTA1_N64 = 7,  /* one CTA per 128x64 tile: twice the CTAs for problems of a few tiles */
+    B200FP8_KERNEL_SKINNY_STREAMK = 8 /* swap-AB stream-K kernel for M <= 128: every SM streams the same share of B,
+                                         partial tiles meet in L2; never chosen automatically (measured slower
+                                         than kernel 4 on B200), kept selectable */
 };
 
 typedef struct b200fp8_options {
     int struct_bytes; /* sizeof(b200fp8_options), for forward compatibility          */
     int depth;        /* shared-memory ring depth: 2, 4, or 0 = as deep as fits      */
     int kernel;       /* B200FP8_KERNEL_*                                            */
-    int split_k;      /* skinny kernel: number of K splits, 0 = automatic            */
+    int split_k;      /* skinny kernels: number of K splits (kernel 4, <= 8) / most pieces
+                         a tile's K range is cut into (kernel 8, <= 64); 0 = automatic */
     int max_ctas;     /* cap on the persistent grid (0 = one CTA per SM); testing    */
 } b200fp8_options;
 
@@ -152,7 +156,7 @@ int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype
  *
  * b200fp8_spmm_bell_rowcol_f32:  C[M][N] = A_sparse[M][K] * B[N][K]^T   (B, C as in the dense operator;
  *                                options->kernel: AUTO, CTA1_N256 or CTA1_N128)
- * b200fp8_spmv_bell_f32:         y[M]    = A_sparse[M][K] * x[K]
+ * b200fp8_spmv_bell_f32:         y[M]    = A_sparse[M][K] * x[K]          (options->kernel: AUTO, SKINNY or SKINNY_STREAMK)
  */
 int b200fp8_gemv_f32(int n, int k, const void* b, int b_dtype, long long ldb, const void* x, int x_dtype, float* y,
                      void* stream);
@@ -197,6 +201,21 @@ int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, 
  */
 int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_dtype, const void* b_host,
                                  int b_dtype, float* c_host, int depth);
+
+/*
+ * Frees the device staging buffers b200fp8_gemm_rowcol_f32_host keeps on the current
+ * device between calls (they grow to the largest problem seen: A, B and C of it).  The
+ * next call allocates again.  Waits for a call in progress on this device.
+ */
+int b200fp8_host_release(void);
+
+/*
+ * Thread safety.  Every entry point may be called from several host threads at once, on the
+ * same or on different devices.  Calls of b200fp8_gemm_rowcol_f32_host on ONE device are
+ * serialised inside the library (they share that device's staging buffers and copy streams);
+ * the device-pointer entry points only enqueue work and share nothing but the small scratch
+ * rings described in INTEGRATION.md.
+ */
 
 /*
  * Seeded synthetic operands: element i (i counted from index_offset) becomes
@@ -271,6 +290,18 @@ long long b200fp8_launch_count(void);
 
 /* "b200fp8 <version> sm_100a" */
 const char* b200fp8_version(void);
+
+#ifdef B200FP8_DIAGNOSTICS
+/*
+ * Only in a library built with -DB200FP8_DIAGNOSTICS (csrc/Makefile, target `diag`): the kernels
+ * then honour the time-stamp and skip bits of the B200FP8_DEBUG environment variable.
+ * b200fp8_debug_trace: DEVICE pointer of the time-stamp buffer, or NULL before the first traced launch.
+ * b200fp8_debug_trace_copy: synchronises the device, copies the first `count` 64-bit words to `dst`,
+ * optionally clears the buffer; returns the number of words copied.
+ */
+void* b200fp8_debug_trace(void);
+int b200fp8_debug_trace_copy(long long* dst, int count, int clear);
+#endif
 
 #ifdef __cplusplus
 }

@@ -39,11 +39,20 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
-def build_ref(reference_root: str = "/root/reference") -> bool:
-    """Build oracle/_ref from the reference sources where they lie; False if absent."""
-    if not os.path.isdir(os.path.join(reference_root, "GEMM")):
+def reference_root() -> str | None:
+    """Root of the reference checkout: $REFERENCE_ROOT, else a directory `reference` beside this repository."""
+    for cand in (os.environ.get("REFERENCE_ROOT"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "GEMM")):
+            return cand
+    return None
+
+
+def build_ref(reference_root_dir: str | None = None) -> bool:
+    """Build oracle/_ref from the reference sources where they lie; False if no reference checkout is found."""
+    reference_root_dir = reference_root_dir or reference_root()
+    if not reference_root_dir or not os.path.isdir(os.path.join(reference_root_dir, "GEMM")):
         return False
-    subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={reference_root}"])
+    subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={reference_root_dir}"])
     return True
 
 

@@ -20,6 +20,7 @@ KERNEL_SKINNY = 4
 KERNEL_PAIR_N512 = 5
 KERNEL_PAIR_N128 = 6
 KERNEL_CTA1_N64 = 7
+KERNEL_SKINNY_STREAMK = 8
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libb200fp8.so")
@@ -36,6 +37,7 @@ DECLARED_SYMBOLS = (
     "b200fp8_spmv_bell_f32",
     "b200fp8_gemm_rowcol_f32_allgather",
     "b200fp8_gemm_rowcol_f32_host",
+    "b200fp8_host_release",
     "b200fp8_gemm_rowcol_f32_noalloc",
     "b200fp8_fill_normal",
     "b200fp8_device_status",
@@ -84,9 +86,11 @@ def build(verbose: bool = False) -> None:
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise FileNotFoundError(f"{LIB_PATH} is not built; run `make -C {CSRC}` (there is no fallback path)")
-        L = ctypes.CDLL(LIB_PATH)
+        # B200FP8_LIBRARY selects another build of the same ABI (the diagnostics build, csrc/Makefile target `diag`)
+        path = os.environ.get("B200FP8_LIBRARY") or LIB_PATH
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} is not built; run `make -C {CSRC}` (there is no fallback path)")
+        L = ctypes.CDLL(path)
         vp, ci, ll, ull = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_ulonglong
         L.b200fp8_gemm_rowcol_f32.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp]
         L.b200fp8_gemm_rowcol_f32_ex.argtypes = [ci, ci, ci, vp, ci, ll, vp, ci, ll, vp, ll,

@@ -13,6 +13,7 @@
 #include "../../include/b200fp8.h"
 #include "gemm_sm100.cuh"
 #include "gemm_skinny_sm100.cuh"
+#include "gemm_skinny_streamk_sm100.cuh"
 #include "fill_fp8.cuh"
 
 namespace b200fp8 {
@@ -32,6 +33,8 @@ struct DeviceCtx {
     void* host_b = nullptr; size_t host_b_bytes = 0;
     void* host_c = nullptr; size_t host_c_bytes = 0;
     cudaStream_t copy_in = nullptr, compute = nullptr, copy_out = nullptr;
+    std::mutex host_mutex;          // serialises the host-pointer entry point on this device (it owns the buffers above)
+    StreamKWorkspace streamk;       // scratch of the stream-K split kernel, allocated at its first launch
 };
 
 std::mutex g_mutex;
@@ -146,7 +149,35 @@ struct Tune {
     }
 };
 const Tune& tune() { static Tune t; return t; }
-long long* g_trace = nullptr;   // diagnostics buffer (B200FP8_DEBUG & 64)
+#ifdef B200FP8_DIAGNOSTICS
+long long* g_trace = nullptr;   // time-stamp buffer of the diagnostics build (B200FP8_DEBUG & (64 | 128 | 1024))
+constexpr int kTraceWords = 3 * 4096;
+long long* trace_buffer() {
+    if (!g_trace && cudaMalloc(&g_trace, kTraceWords * sizeof(long long)) == cudaSuccess)
+        cudaMemset(g_trace, 0, kTraceWords * sizeof(long long));
+    return g_trace;
+}
+#endif
+
+// One workspace slot of the stream-K kernel for the next launch (allocated on first use: four slots of one parked
+// tile and one flag per SM).
+cudaError_t streamk_slot(DeviceCtx& ctx, float4** scratch, unsigned int** flags) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    StreamKWorkspace& w = ctx.streamk;
+    if (w.max_ctas == 0) {
+        for (int i = 0; i < StreamKWorkspace::kSlots; ++i) {
+            cudaError_t e = cudaMalloc(&w.scratch[i], StreamKWorkspace::scratch_bytes(ctx.sm_count));
+            if (e == cudaSuccess) e = cudaMalloc(&w.flags[i], ctx.sm_count * sizeof(unsigned int));
+            if (e == cudaSuccess) e = cudaMemset(w.flags[i], 0, ctx.sm_count * sizeof(unsigned int));
+            if (e != cudaSuccess) return e;
+        }
+        w.max_ctas = ctx.sm_count;
+    }
+    const unsigned int i = w.next++ % StreamKWorkspace::kSlots;
+    *scratch = w.scratch[i];
+    *flags = w.flags[i];
+    return cudaSuccess;
+}
 
 // Blocked-ELL description of A (128 x 128 blocks): column-block indices [ceil(M/128)][blocks] on the device
 struct EllSpec {
@@ -185,10 +216,10 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     args.l2_stores = tune().l2_stores;
     args.debug = tune().debug;
     args.store_gap_ns = (NACC == 1) ? static_cast<unsigned int>(tune().store_gap_ns) : 0u;
-    if (args.debug & (64 | 128)) {
-        if (!g_trace) { cudaMalloc(&g_trace, 3 * 4096 * sizeof(long long)); cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long)); }
-        args.trace = g_trace;
-    }
+#ifdef B200FP8_DIAGNOSTICS
+    if (args.debug & (64 | 128)) args.trace = trace_buffer();
+    if (!args.trace) args.debug &= ~(64 | 128);
+#endif
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
     const int out_bytes = epi ? out_dtype_bytes(epi->out_dtype) : 4;
     // TMA stores clip at 16-byte granularity: a row end that is not a multiple of 16 bytes would spill into the
@@ -294,7 +325,8 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     const int split_k = opt ? opt->split_k : 0;
     const int max_ctas = opt ? opt->max_ctas : 0;
     if (depth != 0 && depth != 2 && depth != 4) return cudaErrorInvalidValue;
-    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_CTA1_N64) return cudaErrorInvalidValue;
+    if (kernel < B200FP8_KERNEL_AUTO || kernel > B200FP8_KERNEL_SKINNY_STREAMK) return cudaErrorInvalidValue;
+    if (split_k > 64) return cudaErrorInvalidValue;
     if (split_k < 0 || max_ctas < 0) return cudaErrorInvalidValue;
 
     DeviceCtx* ctx = nullptr;
@@ -329,10 +361,11 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else if (2 * static_cast<long long>((m + 127) / 128) * n128_cols <= ctx->sm_count) kernel = B200FP8_KERNEL_CTA1_N64;
         else kernel = B200FP8_KERNEL_CTA1_N128;
     }
-    if (kernel == B200FP8_KERNEL_SKINNY && m > kSkinnyMaxM) return cudaErrorInvalidValue;
+    if ((kernel == B200FP8_KERNEL_SKINNY || kernel == B200FP8_KERNEL_SKINNY_STREAMK) && m > kSkinnyMaxM) return cudaErrorInvalidValue;
     if (ell && kernel != B200FP8_KERNEL_CTA1_N256 && kernel != B200FP8_KERNEL_CTA1_N128 && kernel != B200FP8_KERNEL_CTA1_N64)
         return cudaErrorInvalidValue;
-    if (peers && (peers->count > 0 || peers->multicast) && kernel == B200FP8_KERNEL_SKINNY) kernel = B200FP8_KERNEL_PAIR_N256;
+    if (peers && (peers->count > 0 || peers->multicast) && (kernel == B200FP8_KERNEL_SKINNY || kernel == B200FP8_KERNEL_SKINNY_STREAMK))
+        kernel = B200FP8_KERNEL_PAIR_N256;
 
 #define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
 #define B200FP8_LAUNCH4(BN, ST, CT, NA) \
@@ -351,13 +384,27 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         case B200FP8_KERNEL_PAIR_N512:
             return depth == 2 ? B200FP8_LAUNCH4(256, 2, 2, 2) : B200FP8_LAUNCH4(256, 4, 2, 2);
         case B200FP8_KERNEL_SKINNY: {
+            if (split_k > kSkinnyMaxSplits) return cudaErrorInvalidValue;
             long long* trace = nullptr;
-            if (tune().debug & 1024) {                           // diagnostics: eight time stamps per CTA
-                if (!g_trace) { cudaMalloc(&g_trace, 3 * 4096 * sizeof(long long)); cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long)); }
-                if (static_cast<long long>((n + kSkinnyTileN - 1) / kSkinnyTileN) * 8 * 8 <= 3 * 4096) trace = g_trace;
-            }
+#ifdef B200FP8_DIAGNOSTICS
+            if ((tune().debug & 1024) && static_cast<long long>((n + kSkinnyTileN - 1) / kSkinnyTileN) * 8 * 8 <= kTraceWords)
+                trace = trace_buffer();                          // eight time stamps per CTA
+#endif
             e = launch_skinny(ctx->sm_count, ctx->status, g_encode, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype,
                               depth, split_k, epi, stream, nullptr, 0, trace, tune().pdl);
+            if (e == cudaSuccess) ++t_launches;
+            return e;
+        }
+        case B200FP8_KERNEL_SKINNY_STREAMK: {
+            float4* scratch = nullptr;
+            unsigned int* flags = nullptr;
+            if ((e = streamk_slot(*ctx, &scratch, &flags)) != cudaSuccess) return e;
+            long long* trace = nullptr;
+#ifdef B200FP8_DIAGNOSTICS
+            if ((tune().debug & 1024) && ctx->sm_count * 8 <= kTraceWords) trace = trace_buffer();
+#endif
+            e = launch_skinny_streamk(ctx->sm_count, ctx->status, scratch, flags, g_encode, m, k, n, a, lda, b, ldb, c, ldc,
+                                      a_dtype, b_dtype, depth, split_k, epi, stream, nullptr, 0, trace, tune().pdl);
             if (e == cudaSuccess) ++t_launches;
             return e;
         }
@@ -482,8 +529,19 @@ int b200fp8_spmv_bell_f32(int m, int k, const void* ell_values, int a_dtype, lon
     DeviceCtx* ctx = nullptr;
     cudaError_t e = get_ctx(&ctx);
     if (e != cudaSuccess) return e;
-    e = launch_skinny(ctx->sm_count, ctx->status, g_encode, 1, static_cast<int>(width), m, x, k, ell_values, lda, y, m,
-                      x_dtype, a_dtype, depth, split_k, nullptr, st, ell_col_ind, k, nullptr, tune().pdl);
+    if (!(options && options->kernel == B200FP8_KERNEL_SKINNY_STREAMK)) {
+        if (split_k > kSkinnyMaxSplits) return cudaErrorInvalidValue;
+        e = launch_skinny(ctx->sm_count, ctx->status, g_encode, 1, static_cast<int>(width), m, x, k, ell_values, lda, y, m,
+                          x_dtype, a_dtype, depth, split_k, nullptr, st, ell_col_ind, k, nullptr, tune().pdl);
+    } else {
+        if (split_k > 64) return cudaErrorInvalidValue;
+        float4* scratch = nullptr;
+        unsigned int* flags = nullptr;
+        if ((e = streamk_slot(*ctx, &scratch, &flags)) != cudaSuccess) return e;
+        e = launch_skinny_streamk(ctx->sm_count, ctx->status, scratch, flags, g_encode, 1, static_cast<int>(width), m, x, k,
+                                  ell_values, lda, y, m, x_dtype, a_dtype, depth, split_k, nullptr, st, ell_col_ind, k,
+                                  nullptr, tune().pdl);
+    }
     if (e == cudaSuccess) ++t_launches;
     return e;
 }
@@ -516,6 +574,8 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     DeviceCtx* ctx = nullptr;
     cudaError_t e = get_ctx(&ctx);
     if (e != cudaSuccess) return e;
+    // one call at a time per device: the staging buffers and the three streams below belong to the call in progress
+    std::lock_guard<std::mutex> host_lock(ctx->host_mutex);
     if (!ctx->compute) {
         if ((e = cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking)) != cudaSuccess) return e;
         if ((e = cudaStreamCreateWithFlags(&ctx->compute, cudaStreamNonBlocking)) != cudaSuccess) return e;
@@ -603,6 +663,25 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     for (int i = 0; i < bm; ++i) cudaEventDestroy(up_a[i]);
     for (int j = 0; j < bn; ++j) cudaEventDestroy(up_b[j]);
     for (int t = 0; t < bm * bn; ++t) cudaEventDestroy(done[t]);
+    return first;
+}
+
+int b200fp8_host_release(void) {
+    DeviceCtx* ctx = nullptr;
+    cudaError_t e = get_ctx(&ctx);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> host_lock(ctx->host_mutex);
+    cudaError_t first = cudaSuccess;
+    void** bufs[3] = {&ctx->host_a, &ctx->host_b, &ctx->host_c};
+    size_t* sizes[3] = {&ctx->host_a_bytes, &ctx->host_b_bytes, &ctx->host_c_bytes};
+    for (int i = 0; i < 3; ++i) {
+        if (*bufs[i]) {
+            e = cudaFree(*bufs[i]);
+            if (first == cudaSuccess) first = e;
+        }
+        *bufs[i] = nullptr;
+        *sizes[i] = 0;
+    }
     return first;
 }
 
@@ -761,6 +840,12 @@ int b200fp8_device_status(int* status, int reset) {
     if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e;
     if ((e = cudaMemcpy(status, ctx->status, sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess) return e;
     if (reset) e = cudaMemset(ctx->status, 0, sizeof(int));
+    if (reset && *status != 0) {
+        // a kernel that gave up may have left stream-K flags raised: the next launch must find them zero
+        std::lock_guard<std::mutex> lock(g_mutex);
+        for (int i = 0; i < StreamKWorkspace::kSlots && ctx->streamk.max_ctas > 0; ++i)
+            cudaMemset(ctx->streamk.flags[i], 0, ctx->streamk.max_ctas * sizeof(unsigned int));
+    }
     return e;
 }
 
@@ -802,19 +887,21 @@ int b200fp8_ipc_free(void* device_ptr) { return device_ptr ? cudaFree(device_ptr
 
 long long b200fp8_launch_count(void) { return t_launches; }
 
-// diagnostics: device pointer of the k-block timestamp trace (B200FP8_DEBUG & 64), or NULL
+#ifdef B200FP8_DIAGNOSTICS
+// diagnostics build only (declared in include/b200fp8.h under the same macro)
 void* b200fp8_debug_trace(void) { return g_trace; }
 
-// diagnostics: copies the first `count` trace words to the host (after a device synchronise) and, with
+// copies the first `count` trace words to the host (after a device synchronise) and, with
 // `clear`, zeroes the device buffer for the next launch.  Returns the number of words copied (0: no trace).
 int b200fp8_debug_trace_copy(long long* dst, int count, int clear) {
     if (!g_trace || !dst || count <= 0) return 0;
-    if (count > 3 * 4096) count = 3 * 4096;
+    if (count > kTraceWords) count = kTraceWords;
     if (cudaDeviceSynchronize() != cudaSuccess) return 0;
     if (cudaMemcpy(dst, g_trace, static_cast<size_t>(count) * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
-    if (clear) cudaMemset(g_trace, 0, 3 * 4096 * sizeof(long long));
+    if (clear) cudaMemset(g_trace, 0, kTraceWords * sizeof(long long));
     return count;
 }
+#endif
 
 const char* b200fp8_version(void) { return "b200fp8 0.1 sm_100a"; }
 

@@ -47,11 +47,13 @@ struct SkinnyArgs {
     int ell_oob_a, ell_oob_b;   // 128-aligned k coordinates beyond A's K / beyond the compact B
     long long* trace;    // diagnostics: eight globaltimer stamps per CTA (nullptr = off)
     int pdl;             // host only: launch with programmatic stream serialization
+    int l2_prefetch;     // k-blocks of this CTA's first rows of B requested into L2 before the grid dependency wait
     Epilogue epi;        // extended epilogue (alpha, beta, scales, 16-bit output); inactive for the plain operator
 };
 
 // one element of D (column n) under the extended epilogue; `amax` is the thread's running |t| maximum
-__device__ __forceinline__ void skinny_store_epi(const SkinnyArgs& args, float alpha, float dscale, long long idx, int n,
+template <class Args>
+__device__ __forceinline__ void skinny_store_epi(const Args& args, float alpha, float dscale, long long idx, int n,
                                                  float acc, float& amax) {
     float v = alpha * acc;
     if (args.epi.beta != 0.0f) v += args.epi.beta * load_out(args.C, idx, args.epi.out_dtype);
@@ -109,7 +111,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
     volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
 
-    long long* trace = args.trace ? args.trace + 8ll * (blockIdx.y * gridDim.x + blockIdx.x) : nullptr;
+    long long* trace = (kDiagnostics && args.trace) ? args.trace + 8ll * (blockIdx.y * gridDim.x + blockIdx.x) : nullptr;   // diagnostics build only
     if (trace && threadIdx.x == 0) trace[0] = static_cast<long long>(ptx::globaltimer_ns());
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -126,12 +128,25 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         ptx::tmem_alloc<1>(tmem_slot, L::kTmemCols);
         ptx::tmem_relinquish<1>();
     }
+    if (warp == 0 && args.l2_prefetch > 0 && args.ell_col_ind == nullptr) {
+        // The first blocks of B this CTA will stream, requested into L2 before the wait below.  A prefetch changes no
+        // data anywhere (L2 is the point of coherence: a line the previous kernel still writes stays correct); it only
+        // starts the first HBM round trip while the previous kernel of the stream drains.
+        if (ptx::elect_one()) {
+            const int first = blockIdx.y * args.kb_per_split;
+            const int last = min(args.kb_total, first + min(args.kb_per_split, args.l2_prefetch));
+            for (int kb = first; kb < last; ++kb)
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                             ::"l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(kb * kBlockK), "r"(static_cast<int>(blockIdx.x) * kSkinnyTileN) : "memory");
+        }
+        __syncwarp();
+    }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_gen;
-    // Everything above touched only this CTA's own resources and may overlap the previous kernel's tail;
-    // global memory (operands, C, the status word) is touched only after the grids before this one are complete.
+    // Everything above touched only this CTA's own resources (and hinted L2) and may overlap the previous kernel's
+    // tail; global memory (operands, C, the status word) is touched only after the grids before this one are complete.
     ptx::griddep_wait();
     ptx::griddep_launch_dependents();
     if (trace && threadIdx.x == 0) trace[1] = static_cast<long long>(ptx::globaltimer_ns());
@@ -420,6 +435,10 @@ inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, 
     if (epi) args.epi = *epi;
     args.trace = trace;
     args.pdl = pdl;
+    // measured at N = K = 8192 in graphs of back-to-back launches: 8 blocks (128 KiB per CTA) take 0.4-0.5 us off
+    // M <= 16, 0.2 us off M = 64, nothing off M = 128; 16 blocks are no better (B200FP8_SKINNY_L2_PREFETCH overrides)
+    static const int prefetch_env = [] { const char* v = getenv("B200FP8_SKINNY_L2_PREFETCH"); return v ? atoi(v) : 8; }();
+    args.l2_prefetch = pdl ? prefetch_env : 0;
     if (ell_col_ind) {
         args.ell_col_ind = ell_col_ind;
         args.ell_oob_a = (ell_k_small + kBlockK - 1) / kBlockK * kBlockK;

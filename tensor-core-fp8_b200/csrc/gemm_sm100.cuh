@@ -110,6 +110,14 @@ __device__ __forceinline__ void amax_merge_warp(float* amax, float local) {
 
 constexpr int kMaxPeers = 7;         // one box of 8 GPUs
 
+// Diagnostic switches of GemmArgs::debug that alter results or record time stamps exist only in a library built
+// with -DB200FP8_DIAGNOSTICS (csrc/Makefile, target `diag`); the product build compiles them out.
+#ifdef B200FP8_DIAGNOSTICS
+constexpr bool kDiagnostics = true;
+#else
+constexpr bool kDiagnostics = false;
+#endif
+
 struct GemmArgs {
     int M, N, K;
     int num_k_blocks;     // ceil(K / 128)
@@ -127,9 +135,9 @@ struct GemmArgs {
     int l2_stores;        // ... of the FP32 TMA stores of C: 0 none, 2 evict_first
     int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
     uint32_t wait_hint_ns; // suspend-time hint for long mbarrier waits (0 = plain polling)
-    int debug;            // diagnostics only (results become wrong): 1 skip TMA loads, 2 skip C stores, 4 skip MMAs,
-                          // 64 record per-k-block clock64 stamps of CTA 0's MMA warp in `trace`,
-                          // 512 leave the third k-block of every CTA's first tile unloaded (exercises the bounded waits)
+    int debug;            // 512: leave the third k-block of every CTA's first tile unloaded (exercises the bounded waits).
+                          // Diagnostics build only (results become wrong): 1 skip TMA loads, 2 skip C stores, 4 skip MMAs,
+                          // 64 record per-k-block clock64 stamps of CTA 0's MMA warp in `trace`, 128 per-tile start stamps
     float* C;
     long long ldc;
     int* status;          // device status word: 0 = ok, else first error code recorded
@@ -371,7 +379,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     // failure-path test: this ring slot is never armed nor loaded, so the MMA warp's bounded wait on
                     // it must run out and the kernel must end by itself with a status code
                 } else if (ptx::elect_one()) {
-                    if (args.debug & 1) {
+                    if (kDiagnostics && (args.debug & 1)) {
                         if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
                     } else if (pair) {
                         if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
@@ -437,16 +445,16 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     break;
                 }
                 ptx::tc_fence_after();
-                if ((args.debug & 128) && lane == 0 && it < 128) args.trace[(blockIdx.x / CTAS) * 128 + it] = static_cast<long long>(ptx::globaltimer_ns());
+                if (kDiagnostics && (args.debug & 128) && lane == 0 && it < 128) args.trace[(blockIdx.x / CTAS) * 128 + it] = static_cast<long long>(ptx::globaltimer_ns());
                 for (int kb = 0; kb < nkb; ++kb) {
                     long long tr0 = 0, tr1 = 0;
-                    if ((args.debug & 64) && blockIdx.x == 0) tr0 = clock64();
+                    if (kDiagnostics && (args.debug & 64) && blockIdx.x == 0) tr0 = clock64();
                     if (!wait_bounded(bar_full + 8 * s, ph, abort_flag, pair, args.wait_hint_ns)) {
                         record_failure(args.status, abort_flag, kStatusMmaTimeout);
                         ok = false;
                         break;
                     }
-                    if ((args.debug & 64) && blockIdx.x == 0) tr1 = clock64();
+                    if (kDiagnostics && (args.debug & 64) && blockIdx.x == 0) tr1 = clock64();
                     ptx::tc_fence_after();
                     const uint32_t a_src = smem_base + L::kRingOff + s * L::kStageBytes;
                     const uint64_t adesc = ptx::umma_desc_k128(a_src);
@@ -465,7 +473,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         if (ptx::elect_one()) {
 #pragma unroll
                             for (int k = 0; k < kBlockK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
-                                if (!(args.debug & 4)) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                                if (!(kDiagnostics && (args.debug & 4))) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
                         }
                         __syncwarp();
                     }
@@ -475,7 +483,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         else ptx::umma_commit(bar_empty + 8 * s);
                     }
                     __syncwarp();
-                    if ((args.debug & 64) && blockIdx.x == 0 && lane == 0) {
+                    if (kDiagnostics && (args.debug & 64) && blockIdx.x == 0 && lane == 0) {
                         const int idx = it * nkb + kb;
                         if (idx < 4096) { args.trace[3 * idx] = tr0; args.trace[3 * idx + 1] = tr1; args.trace[3 * idx + 2] = clock64(); }
                     }
@@ -609,7 +617,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (issuer) {
-                        if (row0 < args.M && col0 < args.N && !(args.debug & 2) && args.mc_c == nullptr) {
+                        if (row0 < args.M && col0 < args.N && !(kDiagnostics && (args.debug & 2)) && args.mc_c == nullptr) {
                             if (args.l2_stores) ptx::tma_store_2d_hint(&tmap_c, sb, col0, row0, store_policy);
                             else ptx::tma_store_2d(&tmap_c, sb, col0, row0);
                         }

@@ -19,7 +19,8 @@ import torch
 
 from . import _cabi
 from ._cabi import (E4M3, E5M2, KERNEL_AUTO, KERNEL_CTA1_N128, KERNEL_CTA1_N256, KERNEL_PAIR_N256,  # noqa: F401
-                    KERNEL_CTA1_N64, KERNEL_PAIR_N128, KERNEL_PAIR_N512, KERNEL_SKINNY, B200Fp8Error, Options)
+                    KERNEL_CTA1_N64, KERNEL_PAIR_N128, KERNEL_PAIR_N512, KERNEL_SKINNY, KERNEL_SKINNY_STREAMK,
+                    B200Fp8Error, Options)
 
 _DTYPES = {torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
 
@@ -35,11 +36,39 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _gemm(m, k, n, a, b, out, depth, kernel=KERNEL_AUTO, split_k=0, max_ctas=0, lda=None, ldb=None, ldc=None):
+def _check_extent(name: str, t: torch.Tensor, rows: int, cols: int, ld: int) -> None:
+    """The C ABI sees only pointers: a matrix that is too small, transposed or strided along its rows would make a
+    kernel read or write outside the allocation, so the extents are proven here, before the call."""
+    if rows < 0 or cols < 0:
+        raise ValueError(f"{name}: negative extent")
+    if rows == 0 or cols == 0:
+        return
+    if t.dim() > 2 or (t.dim() >= 1 and t.stride(-1) != 1 and t.shape[-1] > 1):
+        raise ValueError(f"{name}: the last dimension must be contiguous (stride 1), got strides {tuple(t.stride())}")
+    if ld < cols:
+        raise ValueError(f"{name}: leading dimension {ld} is smaller than its {cols} columns")
+    need = (rows - 1) * ld + cols
+    # elements reachable from data_ptr(): the tensor's own span (views of larger buffers may carry a pitch)
+    span = 1 + sum((sz - 1) * st for sz, st in zip(t.shape, t.stride())) if t.numel() else 0
+    avail = max(span, (t.shape[0] - 1) * t.stride(0) + (t.shape[1] if t.dim() == 2 else 1) if t.dim() == 2 and t.numel() else span)
+    if need > avail:
+        raise ValueError(f"{name}: needs {need} elements ({rows} rows of {cols}, pitch {ld}) but the tensor spans {avail}")
+
+
+def _check_operands(m, k, n, a, b, out, lda, ldb, ldc, out_name="out"):
     if not (a.is_cuda and b.is_cuda and out.is_cuda):
         raise ValueError("a, b and out must be CUDA tensors (device pointers, as in the reference)")
+    if not (a.device == b.device == out.device):
+        raise ValueError(f"a, b and {out_name} must live on one device, got {a.device}, {b.device}, {out.device}")
+    _check_extent("a", a, m, k, lda)
+    _check_extent("b", b, n, k, ldb)
+    _check_extent(out_name, out, m, n, ldc)
+
+
+def _gemm(m, k, n, a, b, out, depth, kernel=KERNEL_AUTO, split_k=0, max_ctas=0, lda=None, ldb=None, ldc=None):
     if out.dtype != torch.float32:
         raise TypeError("out must be float32")
+    _check_operands(m, k, n, a, b, out, k if lda is None else lda, k if ldb is None else ldb, n if ldc is None else ldc)
     opt = Options(ctypes.sizeof(Options), depth, kernel, split_k, max_ctas)
     with torch.cuda.device(out.device):
         rc = _cabi.lib().b200fp8_gemm_rowcol_f32_ex(
@@ -69,6 +98,8 @@ def gemm_ex(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
         raise ValueError("a and b disagree on K")
     if out is None:
         out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    if tuple(out.shape) != (m, n):
+        raise ValueError(f"out must be [{m}, {n}], got {tuple(out.shape)}")
     return _gemm(m, k, n, a, b, out, depth, kernel, split_k, max_ctas, a.stride(0) if m > 1 else k,
                  b.stride(0) if n > 1 else k, ldc if ldc is not None else (out.stride(0) if m > 1 else n))
 
@@ -93,6 +124,7 @@ def gemm_scaled(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: flo
     for s_ in (a_scale, b_scale):
         if s_ is not None and (s_.dtype != torch.float32 or not s_.is_cuda or s_.numel() != 1):
             raise TypeError("scales are one-element float32 CUDA tensors")
+    _check_operands(m, k, n, a, b, d, a.stride(0) if m > 1 else k, b.stride(0) if n > 1 else k, d.stride(0) if m > 1 else n, "d")
     opt = Options(ctypes.sizeof(Options), depth, kernel, split_k, max_ctas)
     with torch.cuda.device(d.device):
         rc = _cabi.lib().b200fp8_gemm_rowcol_scaled(
@@ -130,6 +162,7 @@ def gemm_epilogue(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: f
             raise TypeError("scales and amax are one-element float32 CUDA tensors")
     if bias is not None and (bias.dtype not in OUT_DTYPES or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous()):
         raise TypeError("bias is a contiguous CUDA vector of N float32 / bfloat16 / float16 values")
+    _check_operands(m, k, n, a, b, d, a.stride(0) if m > 1 else k, b.stride(0) if n > 1 else k, d.stride(0) if m > 1 else n, "d")
     ptr = lambda t: t.data_ptr() if t is not None else None
     ep = _cabi.EpilogueDesc(ctypes.sizeof(_cabi.EpilogueDesc), float(alpha), float(beta), ptr(a_scale), ptr(b_scale),
                             ptr(d_scale), ptr(amax_d), ptr(bias), OUT_DTYPES[bias.dtype] if bias is not None else 0)
@@ -151,6 +184,8 @@ def gemv(b: torch.Tensor, x: torch.Tensor, y: torch.Tensor):
     n, k = b.shape
     if x.numel() != k or y.numel() != n or y.dtype != torch.float32 or not (x.is_contiguous() and y.is_contiguous()):
         raise ValueError("x has K elements, y has N float32 elements, both contiguous")
+    if b.dim() != 2 or (k > 1 and b.stride(1) != 1) or not (b.is_cuda and x.is_cuda and y.is_cuda) or not (b.device == x.device == y.device):
+        raise ValueError("b is a CUDA matrix [N][K] with contiguous rows, on the device of x and y")
     with torch.cuda.device(y.device):
         rc = _cabi.lib().b200fp8_gemv_f32(n, k, b.data_ptr(), dtype_code(b), b.stride(0) if n > 1 else k, x.data_ptr(),
                                            dtype_code(x), y.data_ptr(), _stream_ptr(y.device))
@@ -187,14 +222,15 @@ def spmm_bell(values: torch.Tensor, col_ind: torch.Tensor, b: torch.Tensor, out:
     return out
 
 
-def spmv_bell(values: torch.Tensor, col_ind: torch.Tensor, x: torch.Tensor, y: torch.Tensor, *, split_k: int = 0):
+def spmv_bell(values: torch.Tensor, col_ind: torch.Tensor, x: torch.Tensor, y: torch.Tensor, *, split_k: int = 0,
+              kernel: int = KERNEL_AUTO):
     """y = A_sparse x with A in blocked-ELL form as in spmm_bell; x has K FP8 elements, y has M float32 elements."""
     m = values.shape[0]
     k = x.numel()
     blocks = _check_bell(values, col_ind, m)
     if y.numel() != m or y.dtype != torch.float32 or not (x.is_contiguous() and y.is_contiguous()):
         raise ValueError("y has M float32 elements; x and y are contiguous")
-    opt = Options(ctypes.sizeof(Options), 0, KERNEL_AUTO, split_k, 0)
+    opt = Options(ctypes.sizeof(Options), 0, kernel, split_k, 0)
     with torch.cuda.device(y.device):
         rc = _cabi.lib().b200fp8_spmv_bell_f32(
             m, k, values.data_ptr(), dtype_code(values), values.stride(0) if m > 1 else blocks * ELL_BLOCK,
@@ -207,8 +243,16 @@ def gemm_host(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, depth: int = 
     """BmFN's whole sequence with HOST tensors (GEMM/gemm_main.cpp:56-64, :77, :161): upload, run, download."""
     if a.is_cuda or b.is_cuda or out.is_cuda:
         raise ValueError("gemm_host takes host tensors")
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("a is [M][K], b is [N][K]")
     m, k = a.shape
-    n, _ = b.shape
+    n, k2 = b.shape
+    if k != k2:
+        raise ValueError("a and b disagree on K")
+    if out.dtype != torch.float32 or tuple(out.shape) != (m, n):
+        raise ValueError(f"out must be float32 [{m}, {n}], got {out.dtype} {tuple(out.shape)}")
+    if not (a.is_contiguous() and b.is_contiguous() and out.is_contiguous()):
+        raise ValueError("gemm_host takes contiguous tensors (lda = ldb = K, ldc = N)")
     rc = _cabi.lib().b200fp8_gemm_rowcol_f32_host(m, k, n, a.data_ptr(), dtype_code(a), b.data_ptr(), dtype_code(b),
                                                    out.data_ptr(), depth)
     _cabi.check(rc, f"gemm_host m={m} k={k} n={n}")

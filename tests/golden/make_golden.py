@@ -4,7 +4,7 @@ Needs the reference tree (--ref, default: the REF default of oracle/Makefile) an
 headers; it is run once where those exist and its outputs are committed, so the
 tests themselves never touch the reference tree.
 
-    python tests/golden/make_golden.py [--ref <reference checkout>]
+    python tests/golden/make_golden.py --ref <reference checkout>
 
 What it records:
 
@@ -67,7 +67,7 @@ GEMM_CASES = [
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="root of the reference checkout (its GEMM/ directory is compiled in place)")
     args = ap.parse_args()
 
     subprocess.check_call(["make", "-s", "-C", ORACLE_DIR, "oracle", "ref", f"REF={args.ref}"])

@@ -22,6 +22,7 @@ pytestmark = pytest.mark.gpu
 
 F8 = {0: torch.float8_e4m3fn, 1: torch.float8_e5m2}
 COMBOS = [(0, 0), (1, 1), (0, 1), (1, 0)]
+SKINNY = (4, 8)          # the clustered split-K kernel and the stream-K kernel: both take M <= 128 only
 
 
 @pytest.fixture(scope="module")
@@ -88,10 +89,10 @@ def test_golden_fixture_through_reference_api(g, oracle, path, entry):
 
 # ---------------------------------------------------------------- exact known answers
 
-@pytest.mark.parametrize("kernel", [1, 2, 3, 4, 5, 6, 7])
+@pytest.mark.parametrize("kernel", [1, 2, 3, 4, 5, 6, 7, 8])
 @pytest.mark.parametrize("fa,fb", COMBOS)
 def test_one_hot_rows_select_columns_exactly(g, oracle, kernel, fa, fb):
-    m, k, n = (64, 256, 384) if kernel == 4 else (384, 256, 640)
+    m, k, n = (64, 256, 384) if kernel in SKINNY else (384, 256, 640)
     one = 0x38 if fa == 0 else 0x3C                      # 1.0 in e4m3 / e5m2
     A = np.zeros((m, k), dtype=np.uint8)
     sel = (np.arange(m) * 7 + 3) % k
@@ -103,9 +104,9 @@ def test_one_hot_rows_select_columns_exactly(g, oracle, kernel, fa, fb):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6, 7])
+@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6, 7, 8])
 def test_powers_of_two_sum_exactly(g, oracle, kernel):
-    m, k, n = (128, 512, 256) if kernel == 4 else (256, 512, 512)
+    m, k, n = (128, 512, 256) if kernel in SKINNY else (256, 512, 512)
     rng = np.random.default_rng(5)
     # +-2^e with e in [-2, 2]: every product and every partial sum is exactly representable in FP32
     codes = np.array([0x28, 0x30, 0x38, 0x40, 0x48], dtype=np.uint8)
@@ -135,6 +136,8 @@ def test_special_values_propagate(g, oracle):
     (3, 2, (512, 400, 512)), (3, 4, (300, 208, 516)), (3, 0, (1030, 1024, 770)),
     (5, 2, (512, 400, 1024)), (5, 4, (300, 208, 1030)), (5, 0, (1030, 1024, 1540)),
     (4, 0, (16, 1024, 1000)), (4, 2, (100, 2048, 384)), (4, 4, (128, 528, 260)),
+    (8, 0, (16, 1024, 1000)), (8, 2, (100, 2048, 384)), (8, 4, (128, 528, 260)), (8, 0, (33, 8192 + 16, 130)),
+    (8, 0, (64, 256, 20000)), (8, 0, (1, 128 * 150, 128)), (8, 0, (128, 4096, 2500)),
     (6, 2, (256, 400, 512)), (6, 4, (200, 208, 516)), (6, 0, (700, 1024, 900)),
     (7, 2, (256, 400, 512)), (7, 4, (200, 208, 516)), (7, 0, (700, 1024, 900)),
     (0, 0, (640, 256, 896)),
@@ -172,9 +175,9 @@ def test_ragged_m(g, oracle, m):
 
 
 @pytest.mark.parametrize("k", [16, 32, 48, 64, 112, 128, 144, 256, 4096 + 16])
-@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6, 7])
+@pytest.mark.parametrize("kernel", [2, 3, 4, 5, 6, 7, 8])
 def test_k_sweep_including_tails(g, oracle, k, kernel):
-    m, n = (48, 200) if kernel == 4 else (260, 520)
+    m, n = (48, 200) if kernel in SKINNY else (260, 520)
     a, b = random_operands(g, m, k, n, 0, 1, seed=k)
     out = run(g, a, b, m, k, n, kernel=kernel)
     assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), 0, host_bytes(b), 1)
@@ -182,13 +185,39 @@ def test_k_sweep_including_tails(g, oracle, k, kernel):
 
 @pytest.mark.parametrize("split", [1, 2, 3, 5, 8])
 @pytest.mark.parametrize("m", [1, 24, 128])
-def test_skinny_split_k(g, oracle, split, m):
+@pytest.mark.parametrize("kernel", SKINNY)
+def test_skinny_split_k(g, oracle, split, m, kernel):
     k, n = 2048 + 128, 640
     a, b = random_operands(g, m, k, n, 0, 0, seed=split)
-    out = run(g, a, b, m, k, n, kernel=4, split_k=split)
+    out = run(g, a, b, m, k, n, kernel=kernel, split_k=split)
     assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), 0, host_bytes(b), 0)
-    again = run(g, a, b, m, k, n, kernel=4, split_k=split)
+    again = run(g, a, b, m, k, n, kernel=kernel, split_k=split)
     assert torch.equal(out, again)                       # split-K reduction order is fixed: bitwise repeatable
+
+
+@pytest.mark.parametrize("m,k,n,max_pieces", [(16, 8192, 8192, 0), (128, 8192, 8192, 0), (64, 4096, 1024, 0), (5, 1024, 128, 64),
+                                              (100, 128 * 37, 128 * 5 + 3, 16), (32, 8192, 57344, 0)])
+def test_stream_k_pieces_sum_in_fixed_order(g, oracle, m, k, n, max_pieces):
+    """The stream-K kernel cuts tiles' K ranges between CTAs wherever the even split of the unit space falls; the
+    finisher adds the parked partial sums in ascending K.  Launched repeatedly (the flags a launch raises must come
+    back as zero: no memset between launches) the result must not change by a bit, and it must stay within the
+    path's tolerance of the FP64 oracle on sampled rows and columns."""
+    a, b = random_operands(g, m, k, n, 0, 0, seed=k + n)
+    outs = [run(g, a, b, m, k, n, kernel=8, split_k=max_pieces) for _ in range(3)]
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    cols = np.unique(np.concatenate([np.arange(0, n, max(1, n // 61)), np.arange(max(0, n - 130), n)]))
+    assert_within_tolerance(oracle, np.ascontiguousarray(outs[0][:, torch.from_numpy(cols).cuda()].cpu().numpy()), host_bytes(a), 0,
+                            host_bytes(b)[cols], 0)
+    # power-of-two operands: every partial sum is exact, so the clustered split-K kernel (another split of K
+    # altogether) must agree bit for bit
+    if n <= 8192:
+        rng = np.random.default_rng(m)
+        codes = np.array([0x28, 0x30, 0x38, 0x40], dtype=np.uint8)
+        A = codes[rng.integers(0, 4, size=(m, k))] | (rng.integers(0, 2, size=(m, k), dtype=np.uint8) << 7)
+        B = codes[rng.integers(0, 4, size=(n, k))] | (rng.integers(0, 2, size=(n, k), dtype=np.uint8) << 7)
+        x = run(g, dev_bytes(A, 0), dev_bytes(B, 0), m, k, n, kernel=8, split_k=max_pieces)
+        y = run(g, dev_bytes(A, 0), dev_bytes(B, 0), m, k, n, kernel=4)
+        assert torch.equal(x, y)
 
 
 def test_zero_k_and_empty(g):
@@ -207,6 +236,7 @@ def test_zero_k_and_empty(g):
 @pytest.mark.parametrize("out_dtype,eps", [(torch.float32, 2.0 ** -22), (torch.bfloat16, 2.0 ** -8), (torch.float16, 2.0 ** -11)])
 @pytest.mark.parametrize("kernel,shape,pitch_pad", [(2, (256, 272, 384), 0), (3, (300, 528, 520), 0), (5, (512, 400, 1030), 2),
                                                     (4, (24, 1024, 520), 0), (4, (100, 2048, 384), 0), (1, (130, 144, 259), 1),
+                                                    (8, (24, 1024, 520), 0), (8, (100, 8192, 384), 0), (8, (128, 2048, 2050), 2),
                                                     (3, (512, 256, 512), 8)])
 @pytest.mark.parametrize("beta", [0.0, 0.75])
 def test_scaled_epilogue(g, oracle, out_dtype, eps, kernel, shape, pitch_pad, beta):
@@ -251,7 +281,7 @@ def test_scaled_epilogue_with_unit_factors_equals_plain_operator(g):
 @pytest.mark.parametrize("kernel,m,n,ldc", [(2, 130, 132, 160), (3, 300, 260, 264), (1, 129, 257, 257), (4, 20, 130, 131),
                                             (3, 300, 1030, 1032), (5, 512, 1029, 1032), (1, 130, 259, 260), (2, 130, 130, 132),
                                             (5, 300, 772, 776), (5, 257, 515, 515),
-                                            (4, 100, 260, 272)])
+                                            (4, 100, 260, 272), (8, 20, 130, 131), (8, 100, 260, 272), (8, 128, 1027, 1028)])
 def test_no_write_outside_c(g, oracle, kernel, m, n, ldc):
     k = 192
     a, b = random_operands(g, m, k, n, 0, 0, seed=9)
@@ -298,19 +328,27 @@ def freivalds(a, b, c):
     return worst
 
 
-def sampled_check(oracle, a, b, c, fa, fb, rows=8, cols=8, points=4096):
-    """Full rows, full columns, tile-boundary rows/columns and random points against the FP64 oracle."""
+def sampled_check(oracle, a, b, c, fa, fb, rows=64, cols=64, points=16384):
+    """Sample of a large C against the FP64 oracle, every sampled element over the full K: `rows` random full rows
+    and `cols` random full columns (plus the first, the last and those next to tile edges), the four corner tiles
+    of 128 x 128, and `points` random elements.  Returns the worst error as a fraction of the tolerance."""
     m, k = a.shape
     n = b.shape[0]
     A, B = host_bytes(a), host_bytes(b)
     rng = np.random.default_rng(11)
-    pick_m = sorted(set([0, m - 1] + [x for x in (127, 128, 255, 256) if x < m] + list(rng.integers(0, m, rows))))
-    pick_n = sorted(set([0, n - 1] + [x for x in (127, 128, 255, 256) if x < n] + list(rng.integers(0, n, cols))))
+    edges = (127, 128, 255, 256, 511, 512)
+    pick_m = np.array(sorted(set([0, m - 1] + [x for x in edges if x < m] + list(rng.integers(0, m, rows)))))
+    pick_n = np.array(sorted(set([0, n - 1] + [x for x in edges if x < n] + list(rng.integers(0, n, cols)))))
     worst = 0.0
-    for r in pick_m:
-        worst = max(worst, assert_within_tolerance(oracle, c[r:r + 1].cpu().numpy(), A, fa, B, fb, rows=(r, r + 1)))
-    for col in pick_n:
-        worst = max(worst, assert_within_tolerance(oracle, c[:, col:col + 1].cpu().numpy(), A, fa, B, fb, cols=(col, col + 1)))
+    got = c[torch.from_numpy(pick_m).cuda()].cpu().numpy()                 # full rows, all at once
+    worst = max(worst, assert_within_tolerance(oracle, got, np.ascontiguousarray(A[pick_m]), fa, B, fb))
+    got = np.ascontiguousarray(c[:, torch.from_numpy(pick_n).cuda()].cpu().numpy())   # full columns
+    worst = max(worst, assert_within_tolerance(oracle, got, A, fa, np.ascontiguousarray(B[pick_n]), fb))
+    for r0 in sorted({0, max(0, m - 128)}):                                # corner tiles
+        for c0 in sorted({0, max(0, n - 128)}):
+            got = np.ascontiguousarray(c[r0:r0 + 128, c0:c0 + 128].cpu().numpy())
+            worst = max(worst, assert_within_tolerance(oracle, got, np.ascontiguousarray(A[r0:r0 + 128]), fa,
+                                                       np.ascontiguousarray(B[c0:c0 + 128]), fb))
     ms, ns = rng.integers(0, m, points), rng.integers(0, n, points)
     C64, S = oracle.gemm_f64_points(A, fa, B, fb, ms, ns)
     got = c[torch.from_numpy(ms).cuda(), torch.from_numpy(ns).cuda()].cpu().numpy()
@@ -338,7 +376,10 @@ def test_config2_4096_dtype_sweep(g, oracle, fa, fb, entry):
     getattr(g, entry)(m, k, n, a, b, out)
     torch.cuda.synchronize()
     assert g.device_status() == 0
-    sampled_check(oracle, a, b, out, fa, fb)
+    if (fa, fb) == (0, 0) and entry == "GEMM":
+        assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), fa, host_bytes(b), fb)   # every element
+    else:
+        sampled_check(oracle, a, b, out, fa, fb)
     assert freivalds(a, b, out) <= 1.0
 
 
@@ -348,7 +389,7 @@ def test_config3_large_shapes(g, oracle, shape):
     m, k, n = shape
     a, b = random_operands(g, m, k, n, 0, 0, seed=0xB200F800 + 48)
     out = run(g, a, b, m, k, n)
-    sampled_check(oracle, a, b, out, 0, 0, rows=4, cols=4, points=2048)
+    sampled_check(oracle, a, b, out, 0, 0)
     assert freivalds(a, b, out) <= 1.0
 
 
@@ -359,7 +400,7 @@ def test_config4_skinny_decode_shapes(g, oracle, m, k, n):
     if m * n <= 16 * 8192:
         assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), 0, host_bytes(b), 0)   # exhaustive
     else:
-        sampled_check(oracle, a, b, out, 0, 0, rows=4, cols=16, points=4096)
+        sampled_check(oracle, a, b, out, 0, 0, rows=16, cols=64)
     assert freivalds(a, b, out) <= 1.0
 
 
@@ -387,8 +428,21 @@ def test_config5_full_size_one_rank_shard(g, oracle):
     n = 4096
     a, b = random_operands(g, m, k, n, 0, 0, seed=0xB200F800 + 80)
     out = run(g, a, b, m, k, n)
-    sampled_check(oracle, a, b, out, 0, 0, rows=2, cols=2, points=2048)
+    sampled_check(oracle, a, b, out, 0, 0, rows=16, cols=16)
     assert freivalds(a, b, out) <= 1.0
+
+
+def test_config5_full_size_single_gpu_headline_problem(g, oracle):
+    """The benchmark's N = 1 problem as it is timed: 32768^3 in one call (selects the 256 x 512 pair tile with tile
+    pacing).  6.4 GB on the device; sampled rows, columns, corner tiles and points through the FP64 oracle, and every
+    element through the randomised product check."""
+    m = k = n = 32768
+    a, b = random_operands(g, m, k, n, 0, 0, seed=0xB200F800 + 64)
+    out = run(g, a, b, m, k, n)
+    sampled_check(oracle, a, b, out, 0, 0, rows=16, cols=16, points=16384)
+    assert freivalds(a, b, out) <= 1.0
+    del out
+    torch.cuda.empty_cache()
 
 
 # ---------------------------------------------------------------- size-independent properties at large sizes

@@ -91,13 +91,14 @@ def test_spmm_without_blocks_is_zero_and_bad_arguments_are_refused(g, oracle):
 @pytest.mark.parametrize("fa,fx", [(0, 0), (1, 1), (0, 1)])
 @pytest.mark.parametrize("m,k,blocks,split_k", [(1024, 4096, 8, 0), (300, 1040, 5, 0), (128, 128 * 80, 70, 1), (8192, 8192, 16, 0),
                                                 (130, 256, 1, 0), (4096, 128 * 96, 96, 2)])
-def test_spmv_against_oracle(g, oracle, fa, fx, m, k, blocks, split_k):
+@pytest.mark.parametrize("kernel", [0, 8], ids=["clustered", "stream-k"])
+def test_spmv_against_oracle(g, oracle, fa, fx, m, k, blocks, split_k, kernel):
     vals, ind = oracle.make_bell_uniform(m, k, blocks, fa, seed=m + blocks, sigma=2.0 if fa else 1.0)
     if blocks > 2:
         ind[0, -1] = -1                 # one padding block
     x = oracle.fill_normal(k, fx, 2.0 if fx else 1.0, 3).reshape(1, k)
     y = torch.full((m,), float("nan"), dtype=torch.float32, device="cuda")
-    g.spmv_bell(dev(vals, fa), torch.from_numpy(ind).cuda(), dev(x, fx).reshape(k), y, split_k=split_k)
+    g.spmv_bell(dev(vals, fa), torch.from_numpy(ind).cuda(), dev(x, fx).reshape(k), y, split_k=split_k, kernel=kernel)
     torch.cuda.synchronize()
     assert g.device_status() == 0
     dense = oracle.bell_to_dense(vals, ind, k)
