@@ -258,7 +258,8 @@ int b200fp8_device_status(int* status, int reset);
  *     stream, or otherwise keep them from overlapping;
  *   - the first call on each device resolves the array's device address and
  *     prepares the kernels; make that first call outside any stream capture;
- *   - at most 2^24 output tiles (256 x 256 elements each) per call; larger
+ *   - at most 2^24 output tiles per call (a tile is 256 x 256 elements, or
+ *     256 x 512 for the large problems that take the wide-tile kernel); larger
  *     problems are rejected with cudaErrorInvalidValue and a message on stderr.
  * Always runs a CTA-pair kernel, whatever the shape.  `status_word` is an
  * optional DEVICE int the caller owns and has zeroed: a kernel whose bounded

@@ -20,11 +20,17 @@ def pkg():
 
 def test_header_symbols_exported(pkg):
     header = open(os.path.join(ROOT, "include", "b200fp8.h")).read()
-    declared = set(re.findall(r"\b(b200fp8_[a-z0-9_]+)\s*\(", header))
+    diag = re.findall(r"#ifdef B200FP8_DIAGNOSTICS(.*?)#endif", header, flags=re.S)
+    product = re.sub(r"#ifdef B200FP8_DIAGNOSTICS.*?#endif", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(b200fp8_[a-z0-9_]+)\s*\(", product))
     assert declared == set(pkg._cabi.DECLARED_SYMBOLS), declared ^ set(pkg._cabi.DECLARED_SYMBOLS)
     lib = pkg._cabi.lib()
     for sym in declared:
         assert getattr(lib, sym) is not None
+    # what the header declares only for the diagnostics build is absent from the product library
+    out = subprocess.run(["nm", "-D", "--defined-only", pkg._cabi.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    for sym in re.findall(r"\b(b200fp8_[a-z0-9_]+)\s*\(", "".join(diag)):
+        assert sym not in out, sym
 
 
 def test_reference_operator_symbols_exported(pkg):
@@ -89,3 +95,31 @@ def test_column_shards_partition_n(pkg):
     assert [p.n for p in sh.all_shards(32768, 8)] == [4096] * 8
     with pytest.raises(ValueError):
         sh.column_shard(10, 3, 2)
+
+
+def test_python_wrappers_reject_bad_extents_before_the_call(pkg):
+    """The C ABI sees only pointers, so the wrappers prove shapes, strides and extents first (no GPU needed: the
+    checks come before the library call)."""
+    import torch
+    g = pkg.gemm
+    t = torch.empty((4, 8))
+    g._check_extent("t", t, 4, 8, 8)                                   # exact fit
+    g._check_extent("view", torch.empty((4, 16))[:, :8], 4, 8, 16)     # a column block of a wider matrix (pitch 16)
+    with pytest.raises(ValueError):
+        g._check_extent("transposed", t.t(), 8, 4, 4)                  # rows are not contiguous
+    with pytest.raises(ValueError):
+        g._check_extent("short", t, 5, 8, 8)                           # one row more than the tensor holds
+    with pytest.raises(ValueError):
+        g._check_extent("pitch", t, 4, 8, 4)                           # pitch smaller than a row
+    a = torch.empty((8, 32), dtype=torch.uint8).view(torch.float8_e4m3fn)
+    b = torch.empty((16, 32), dtype=torch.uint8).view(torch.float8_e4m3fn)
+    with pytest.raises(ValueError):
+        g.gemm_ex(a, b, torch.empty((8, 16)))                          # host tensors: the operator takes device pointers
+    with pytest.raises(ValueError):
+        g.gemm_host(a, b, torch.empty((8, 15)))                        # out has the wrong shape
+    with pytest.raises(ValueError):
+        g.gemm_host(a, b, torch.empty((8, 16), dtype=torch.float64))   # out has the wrong dtype
+    with pytest.raises(ValueError):
+        g.gemm_host(a, b[:, :16], torch.empty((8, 16)))                # K mismatch
+    with pytest.raises(ValueError):
+        g.gemm_host(a, torch.empty((16, 64), dtype=torch.uint8).view(torch.float8_e4m3fn)[:, :32], torch.empty((8, 16)))  # not contiguous

@@ -62,3 +62,53 @@ def test_concurrent_host_threads_on_own_streams_match_sequential_results(g):
     assert not errors, errors
     torch.cuda.synchronize()
     assert g.device_status() == 0
+
+
+def test_host_entry_point_from_two_threads_with_growing_sizes(g):
+    """`b200fp8_gemm_rowcol_f32_host` owns per-device staging buffers that grow to the largest problem seen.  Two host
+    threads calling it at once on one device, one of them with ever larger problems (so that the buffers are
+    re-allocated while the other thread is active), must each get exactly the device entry point's result: calls
+    on one device are serialised inside the library.  `b200fp8_host_release` between calls frees the buffers."""
+    pkg = load_package()
+    lib = pkg._cabi.lib()
+    f8 = torch.float8_e4m3fn
+    plans = [[(256, 512, 384), (512, 1024, 768), (1024, 1024, 2048), (2048, 2048, 2048)],
+             [(300, 272, 520), (300, 272, 520), (64, 1024, 512), (1536, 512, 1024)]]
+    work = []
+    for t, shapes in enumerate(plans):
+        items = []
+        for i, (m, k, n) in enumerate(shapes):
+            a = torch.empty((m, k), dtype=f8, device="cuda")
+            b = torch.empty((n, k), dtype=f8, device="cuda")
+            g.fill_normal(a, 1.0, 300 + 10 * t + i)
+            g.fill_normal(b, 1.0, 400 + 10 * t + i)
+            want = torch.empty((m, n), dtype=torch.float32, device="cuda")
+            g.gemm_ex(a, b, want)
+            torch.cuda.synchronize()
+            items.append((a.cpu(), b.cpu(), want.cpu()))
+        work.append(items)
+    errors = []
+
+    def worker(t):
+        try:
+            torch.cuda.set_device(0)
+            for rnd in range(3):
+                for (ha, hb, want) in work[t]:
+                    out = torch.full(want.shape, float("nan"), dtype=torch.float32)
+                    g.gemm_host(ha, hb, out)
+                    if not torch.equal(out, want):
+                        errors.append(f"thread {t}: result differs at {tuple(want.shape)}")
+                        return
+                if t == 1 and lib.b200fp8_host_release() != 0:
+                    errors.append("host_release failed")
+        except Exception as e:
+            errors.append(f"thread {t}: {e!r}")
+
+    threads = [threading.Thread(target=worker, args=(t,)) for t in range(2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join(timeout=300)
+    assert not any(th.is_alive() for th in threads)
+    assert not errors, errors
+    assert g.device_status() == 0
