@@ -14,6 +14,16 @@ Workloads (synthetic operands, N(0,1) cast to e4m3 with RNE + saturate-to-finite
 A step is one operator call on operands resident in HBM.  `value` is whole-job TFLOPS over all
 GPUs from the max-over-ranks device time; `e2e` is the same quantity through the host-pointer
 entry point (pinned host buffers, uploads and the download of C inside the timed region).
+
+Beside the headline the default run reports, in the same line:
+    parity      the C buffer that was timed, checked after the timed region (FP64 oracle on sampled rows, columns and
+                points over the full K; a randomised product check of every element on the device)
+    configs     (N = 1) every other benchmark configuration -- 1024^3, 4096^3 x 4 dtype pairs x ring depths, 8192^3,
+                the FFN shapes, the decode shapes -- each timed as CUDA graphs over rotating buffers, alternating with
+                cuBLASLt on the same buffers, with the parity of its own timed buffer
+    side        (N = 1) the reference's own kernels where they build for sm_100 (time only)
+    sustained, allgather, fused_allgather   (N > 1) a one-second steady-state leg per GPU, the NCCL all-gather of the C
+                blocks, and the GEMM with the all-gather fused into its epilogue, each with its own parity
 `--impl reference` times the reference's own CPU implementation of the path (its verification
 loop, GEMM/gemm_main.cpp:45-52, as restated by the oracle) on all host threads over a bounded
 sample of the same workload.
@@ -56,12 +66,10 @@ SPARSE_WORKLOADS = {
 SEED_BASE = 0xB200F800
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under profiles/
-NCU_TRAFFIC_BYTES = {
-    "shard32768": 30.11e9,   # profiles/gemm_fp8_rowcol_kernel__shard32768__launch_list_and_dram.md
-    "gemm8192": 537.6e6,     # profiles/gemm_fp8_rowcol_kernel__gemm8192__full_set.md
-    "skinny16": 67.8e6,      # profiles/gemm_fp8_skinny_kernel__skinny16__full_set.md
-}
+NVLINK_PEER_COPY_GBS = 770.0      # measured peer-copy rate per direction per GPU on this pool (nominal 900)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from one ncu capture at N = 1
+NCU_TRAFFIC_BYTES = {"shard32768": 30.11e9, "gemm8192": 537.6e6, "skinny16": 67.8e6}
+DTYPE_NAMES = {0: "e4m3", 1: "e5m2"}
 
 
 def measured_peaks():
@@ -138,11 +146,20 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+def host_threads() -> int:
+    """Host threads this process may run on.  Launchers for multi-rank runs export OMP_NUM_THREADS=1, which would make
+    the CPU arm a single-thread run: the team is sized from the scheduler's affinity mask instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_reference_rate(M, K, N, rows_per_thread: int, seed_a: int, seed_b: int):
     """The reference's CPU loop (oracle port) on a bounded sample: returns (TFLOPS, threads, description, seconds)."""
     import numpy as np
     from oracle import fp8_oracle as fo
-    threads = fo.max_threads()
+    threads = host_threads()
     rows = min(M, rows_per_thread * threads)
     cols = min(N, 512)
     A = fo.fill_normal(rows * K, fo.E4M3, 1.0, seed_a).reshape(rows, K)
@@ -163,6 +180,7 @@ def reference_binary_rate(size: int = 512):
     exe = os.path.join(ROOT, "oracle", "_ref", "ref_gemm_cpu")
     if not os.path.exists(exe):
         return None
+
     def run(verify):
         t0 = time.perf_counter()
         subprocess.run([exe, str(size), str(size), str(size), "2", str(verify), "0", "0"], check=True,
@@ -181,6 +199,29 @@ def reference_binary_rate(size: int = 512):
                       "(run with verify = 1 minus run with verify = 0)"}
 
 
+def workload_config(args, M, K, N, n_local, world, sharded, l2, timing):
+    """The `config` object: the same keys and, for one workload and N, the same values in both arms."""
+    return {"workload": args.workload, "M": M, "K": K, "N": N, "n_per_rank": n_local, "layout": "row-col",
+            "a": args.a_dtype, "b": args.b_dtype, "out": "f32",
+            "parallelism": f"n-shard x{world}" if sharded else f"replicas x{world}", "l2": l2,
+            "kernel": args.kernel, "depth": args.depth, "timing": timing}
+
+
+def describe_l2(nsets):
+    return "inputs larger than L2" if nsets == 1 else f"rotating over {nsets} distinct B/C buffer sets larger than L2"
+
+
+def operand_sets(M, K, n_local):
+    bytes_per_set = n_local * K + 4 * M * n_local
+    return 1 if (M * K + bytes_per_set) > (512 << 20) else max(2, min(8, (1 << 30) // max(1, bytes_per_set)))
+
+
+def graph_timed(M, K, n_local):
+    # Short steps are launch-bound when driven call by call from Python, so their K steps are captured
+    # once in a CUDA graph and replayed; long steps are timed launch by launch.
+    return 2.0 * M * K * n_local < 2e12
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -189,6 +230,12 @@ def run_reference(args):
         M, K, N, sharded = SPARSE_WORKLOADS[args.workload][1:4] + (False,)
     else:
         M, K, N, sharded = WORKLOADS[args.workload]
+    world = max(1, args.gpus)
+    if sharded:
+        from __graft_entry__ import load_package
+        n_local = load_package().shard.column_shard(N, 0, world).n
+    else:
+        n_local = N
     # bounded sample per step: about a second of work per step on all host threads
     rates = []
     for i in range(args.warmup + args.steps):
@@ -202,8 +249,9 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_t / len(rates),
         "higher_is_better": True, "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "fp8",
         "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "layout": "row-col", "a": "e4m3", "b": "e4m3",
-                   "out": "f32"},
+        # the GPU arm's description of the same problem (the CPU arm runs a bounded sample of it, see cpu_baseline)
+        "config": workload_config(args, M, K, N, n_local, world, sharded, describe_l2(operand_sets(M, K, n_local)),
+                                  "one CUDA graph of all steps, replayed" if graph_timed(M, K, n_local) else "launch by launch"),
         "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port",
                          "sample": "each step: " + sample + "; the reference's float loop "
                                    "(GEMM/gemm_main.cpp:45-52) restated in oracle/fp8_oracle.c, OpenMP over rows"},
@@ -215,6 +263,274 @@ def run_reference(args):
         line["cpu_baseline"]["reference_loop"] = ref_loop
     print(json.dumps(line))
     return 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# parity of a timed buffer
+# ---------------------------------------------------------------------------------------------------------------
+
+def freivalds(torch, a, b, c, n_cols=None):
+    """C r against A (B^T r) in FP64 on the device, bound = the summed per-element tolerance: covers every element."""
+    n = b.shape[0]
+    dev = a.device
+    gen = torch.Generator(device=dev).manual_seed(7)
+    r = (torch.randint(0, 2, (n,), device=dev, generator=gen).double() * 2 - 1)
+    worst = 0.0
+    btr = torch.zeros(b.shape[1], dtype=torch.float64, device=dev)
+    babs = torch.zeros_like(btr)
+    for n0 in range(0, n, 4096):
+        blk = b[n0:n0 + 4096].double()
+        btr += blk.T @ r[n0:n0 + 4096]
+        babs += blk.abs().sum(dim=0)
+        del blk
+    for m0 in range(0, a.shape[0], 4096):
+        ablk = a[m0:m0 + 4096].double()
+        want = ablk @ btr
+        bound = 1e-3 * (ablk.abs() @ babs) + 1e-6 * n
+        got = c[m0:m0 + 4096].double() @ r
+        worst = max(worst, float(((got - want).abs() / bound).max()))
+        del ablk
+    return worst
+
+
+def parity_of(torch, g, a, b, c, rows=8, cols=8, points=4096):
+    """Checks a C buffer the benchmark has just timed: `rows` full rows, `cols` full columns and `points` random
+    elements against the FP64 oracle (|C - C_ref| <= 1e-3 * sum_k |a b| + 1e-6, every sampled element over the full
+    K), and every element through the randomised product check on the device.  `worst` is the largest error as a
+    fraction of the tolerance over both: <= 1 passes."""
+    import numpy as np
+    from oracle import fp8_oracle as fo
+    t0 = time.perf_counter()
+    m, k = a.shape
+    n = b.shape[0]
+    fa, fb = g.dtype_code(a), g.dtype_code(b)
+    dev = a.device
+    rng = np.random.default_rng(11)
+    pick_m = np.unique(np.concatenate([[0, m - 1], rng.integers(0, m, rows)]))
+    pick_n = np.unique(np.concatenate([[0, n - 1], rng.integers(0, n, cols)]))
+    ms, ns = rng.integers(0, m, points), rng.integers(0, n, points)
+    tm, tn = torch.from_numpy(pick_m).to(dev), torch.from_numpy(pick_n).to(dev)
+    a8, b8 = a.view(torch.uint8), b.view(torch.uint8)
+    worst, bad = 0.0, 0
+    # full rows: A's sampled rows against all of B (B comes to the host once; A only in the sampled rows)
+    B = b8.cpu().numpy()
+    C64, S = fo.gemm_f64(np.ascontiguousarray(a8[tm].cpu().numpy()), fa, B, fb)
+    nb, w, _ = fo.check_tolerance(c[tm].cpu().numpy(), C64, S)
+    bad, worst = bad + int(nb), max(worst, float(w))
+    A = a8.cpu().numpy()
+    C64, S = fo.gemm_f64(A, fa, np.ascontiguousarray(B[pick_n]), fb)
+    nb, w, _ = fo.check_tolerance(np.ascontiguousarray(c[:, tn].cpu().numpy()), C64, S)
+    bad, worst = bad + int(nb), max(worst, float(w))
+    C64, S = fo.gemm_f64_points(A, fa, B, fb, ms, ns)
+    nb, w, _ = fo.check_tolerance(c[torch.from_numpy(ms).to(dev), torch.from_numpy(ns).to(dev)].cpu().numpy(), C64, S)
+    bad, worst = bad + int(nb), max(worst, float(w))
+    del A, B
+    fr = freivalds(torch, a, b, c)
+    return {"worst": max(worst, fr), "oracle_worst": worst, "elements_outside_tolerance": bad, "freivalds": fr,
+            "sample": f"{len(pick_m)} rows + {len(pick_n)} columns + {points} points (FP64 oracle, full K); every element "
+                      "by the randomised product check", "seconds": round(time.perf_counter() - t0, 2)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the other benchmark configurations, ours alternating with cuBLASLt on the same buffers
+# ---------------------------------------------------------------------------------------------------------------
+
+class Comparator:
+    """cuBLASLt FP8 through the separate comparator library (never part of libb200fp8.so)."""
+
+    def __init__(self, path):
+        self.lib = ctypes.CDLL(path) if os.path.exists(path) else None
+        if self.lib is not None:
+            ci, vp, fp = ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)
+            self.lib.b200fp8_cmp_cublaslt.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci, fp, ctypes.POINTER(ci), vp]
+            self.lib.b200fp8_cmp_cublaslt_enqueue.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp]
+
+    def choose(self, m, k, n, a, fa, b, fb, c, stream):
+        """Picks the fastest of cuBLASLt's candidates for the shape; False when it offers none (e5m2 x e5m2)."""
+        if self.lib is None:
+            return False
+        ms, found = ctypes.c_float(-1), ctypes.c_int(0)
+        return self.lib.b200fp8_cmp_cublaslt(m, k, n, a.data_ptr(), fa, b.data_ptr(), fb, c.data_ptr(), 3, 8, 0,
+                                             ctypes.byref(ms), ctypes.byref(found), stream) == 0
+
+    def enqueue(self, m, k, n, a, fa, b, fb, c, stream):
+        return self.lib.b200fp8_cmp_cublaslt_enqueue(m, k, n, a.data_ptr(), fa, b.data_ptr(), fb, c.data_ptr(), stream)
+
+
+def measure_config(torch, g, cmp, dev, name, M, K, N, fa, fb, depth, kernel, peaks, check=True, seed=0):
+    """One configuration on one GPU.  Ours and cuBLASLt each as a CUDA graph of `iters` launches over rotating B/C
+    buffers larger than L2 (long steps: launch by launch), four alternating rounds of lead-in + timed replay, the
+    first round dropped.  Then the parity of C buffer 0, which every timed replay rewrote."""
+    f8 = {0: torch.float8_e4m3fn, 1: torch.float8_e5m2}
+    nsets = operand_sets(M, K, N)
+    a = torch.empty((M, K), dtype=f8[fa], device=dev)
+    g.fill_normal(a, 2.0 if fa else 1.0, SEED_BASE + 128 + seed)
+    bs, cs = [], []
+    for i in range(nsets):
+        b = torch.empty((N, K), dtype=f8[fb], device=dev)
+        g.fill_normal(b, 2.0 if fb else 1.0, SEED_BASE + 129 + seed + 1000 * i)
+        bs.append(b)
+        cs.append(torch.empty((M, N), dtype=torch.float32, device=dev))
+    flops = 2.0 * M * K * N
+    nbytes = float(M * K + N * K + 4 * M * N)
+    est = max(flops / 2.5e15, nbytes / 5e12, 4e-6)
+    iters = int(max(4, min(48, 2.5e-3 / est)))
+    long_step = flops >= 2e12
+    if long_step:
+        iters = 6
+    stream = torch.cuda.current_stream().cuda_stream
+    have_cmp = cmp.choose(M, K, N, a, fa, bs[0], fb, cs[0], stream)
+
+    def ours(i, _cap=None):
+        g.gemm_ex(a, bs[i % nsets], cs[i % nsets], depth=depth, kernel=kernel)
+
+    def theirs(i, cap=None):
+        cmp.enqueue(M, K, N, a, fa, bs[i % nsets], fb, cs[i % nsets], cap or stream)
+
+    def as_graph(fn):
+        for i in range(2):
+            fn(i)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            cap = torch.cuda.current_stream().cuda_stream
+            for i in range(iters):
+                fn(i, cap)
+        return gr.replay
+
+    def as_loop(fn):
+        def run():
+            for i in range(iters):
+                fn(i)
+        return run
+
+    wrap = as_loop if long_step else as_graph
+    run_ours = wrap(ours)
+    run_theirs = wrap(theirs) if have_cmp else None
+    t_ours, t_theirs = [], []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rnd in range(4):
+        for run, acc in ((run_ours, t_ours), (run_theirs, t_theirs)):
+            if run is None:
+                continue
+            run()                                   # lead-in: clocks and caches settle to THIS kernel's steady state
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            if rnd:
+                acc.append(e0.elapsed_time(e1) / iters)
+    if have_cmp:                                    # the last writer of the buffers must be OUR kernel: parity is of our C
+        run_ours()
+        torch.cuda.synchronize()
+    status = g.device_status()
+    ms = sum(t_ours) / len(t_ours)
+    row = {"M": M, "K": K, "N": N, "a": DTYPE_NAMES[fa], "b": DTYPE_NAMES[fb], "depth": depth, "kernel": kernel,
+           "ms": ms, "tflops": flops / ms / 1e9, "gbs": nbytes / ms / 1e6,
+           "timing": ("launch by launch" if long_step else f"CUDA graph of {iters} launches")
+                     + f" over {nsets} rotating B/C sets, 3 alternating rounds", "launches_per_replay": iters,
+           "device_status": status}
+    if M <= 128:
+        row.update({"bound": "hbm", "frac": row["gbs"] / peaks["hbm_gbs"], "peak": peaks["hbm_gbs"], "peak_unit": "GB/s",
+                    "frac_of_nominal_8TBs": row["gbs"] / NOMINAL_HBM_GBS})
+    else:
+        peak = 2.0 * peaks["bf16_burst"]            # a few milliseconds of launches: the burst figure applies
+        row.update({"bound": "tensor", "frac": row["tflops"] / peak, "peak": peak, "peak_unit": "TFLOP/s (2 x burst cuBLAS bf16)",
+                    "frac_of_nominal_4500": row["tflops"] / NOMINAL_FP8_TFLOPS})
+    if t_theirs:
+        t = sum(t_theirs) / len(t_theirs)
+        row.update({"cublaslt_ms": t, "vs_cublaslt": t / ms})
+    else:
+        row.update({"cublaslt_ms": None, "vs_cublaslt": None,
+                    "cublaslt_note": "no cuBLASLt kernel for this dtype pair" if cmp.lib is not None else "comparator library not built"})
+    if check:
+        row["parity"] = parity_of(torch, g, a, bs[0], cs[0], rows=8, cols=8, points=2048)
+    del a, bs, cs
+    torch.cuda.empty_cache()
+    return row
+
+
+def run_configs(torch, g, cmp, dev, peaks, budget_s=150.0):
+    """Every benchmark configuration other than the headline.  Short ones first: after the power-capped long runs the
+    clocks need a while to recover."""
+    combos = [(0, 0), (1, 1), (0, 1), (1, 0)]
+    plan = []
+    for m in (1, 16, 64, 128):
+        plan.append((f"decode_m{m}_8192x8192", m, 8192, 8192, 0, 0, 0, 0))
+    plan.append(("decode_m32_n57344_k8192", 32, 8192, 57344, 0, 0, 0, 0))
+    for depth in (2, 4, 0):
+        plan.append((f"gemm1024_depth{depth}", 1024, 1024, 1024, 0, 0, depth, 0))
+    for (fa, fb) in combos:
+        for depth in (2, 4, 0):
+            plan.append((f"gemm4096_{DTYPE_NAMES[fa]}x{DTYPE_NAMES[fb]}_depth{depth}", 4096, 4096, 4096, fa, fb, depth, 0))
+    plan.append(("m256_8192x8192", 256, 8192, 8192, 0, 0, 0, 0))
+    plan.append(("m512_8192x8192", 512, 8192, 8192, 0, 0, 0, 0))
+    plan.append(("gemm8192", 8192, 8192, 8192, 0, 0, 0, 0))
+    plan.append(("ffn_up_8192x8192x28672", 8192, 8192, 28672, 0, 0, 0, 0))
+    plan.append(("ffn_down_8192x28672x8192", 8192, 28672, 8192, 0, 0, 0, 0))
+    out, t0 = {}, time.perf_counter()
+    for idx, (name, M, K, N, fa, fb, depth, kernel) in enumerate(plan):
+        if time.perf_counter() - t0 > budget_s:
+            out[name] = {"skipped": "time budget of the configs leg spent"}
+            continue
+        out[name] = measure_config(torch, g, cmp, dev, name, M, K, N, fa, fb, depth, kernel, peaks, seed=2 * idx)
+    worst = [r["parity"]["worst"] for r in out.values() if "parity" in r]
+    summary = {"rows": len(out), "measured": len(worst), "parity_worst": max(worst) if worst else None,
+               "all_within_tolerance": bool(worst) and max(worst) <= 1.0, "seconds": round(time.perf_counter() - t0, 1)}
+    return out, summary
+
+
+def reference_kernels_side(torch, g, dev):
+    """The reference's own mma.sync kernels (built unmodified from a scratch copy without its unbuildable kernel 2,
+    baseline/Makefile) with the reference driver's protocol (GEMM/gemm_main.cpp:25-26, :69-84: 20 warm-up calls, then
+    100 calls each bracketed by events and synchronised, mean).  Time only: the kernels never zero their accumulators
+    and write full 128 x 128 tiles only, so their C is not checked.  Ours runs with the same protocol beside them."""
+    path = os.path.join(ROOT, "baseline", "_ref", "libref_kernels.so")
+    if not os.path.exists(path):
+        return {"unavailable": "baseline/_ref/libref_kernels.so is not built (needs the reference checkout at build time)"}
+    lib = ctypes.CDLL(path)
+    ci, vp = ctypes.c_int, ctypes.c_void_p
+    entries = {"kernel1_e4m3xe4m3 (GEMM/src/gemm.cu:29-262)": ("_ZN4gemm4GEMMEiiiPK13__nv_fp8_e4m3S2_Pf", torch.float8_e4m3fn, 1.0),
+               "kernel3_e5m2xe5m2 (GEMM/src/gemm.cu:696-921)": ("_ZN4gemm4GEMMEiiiPK13__nv_fp8_e5m2S2_Pf", torch.float8_e5m2, 2.0)}
+    out = {"protocol": "20 warm-up calls, 100 calls individually timed with events and synchronised, mean "
+                       "(GEMM/gemm_main.cpp:69-84); legacy default stream; results of the reference kernels not checked"}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def protocol(call):
+        for _ in range(20):
+            call()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(100):
+            e0.record()
+            call()
+            e1.record()
+            e1.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / 100
+
+    for size in (4096, 8192):
+        for label, (sym, dt, sigma) in entries.items():
+            fn = getattr(lib, sym)
+            fn.argtypes = [ci, ci, ci, vp, vp, vp]
+            a = torch.empty((size, size), dtype=dt, device=dev)
+            b = torch.empty((size, size), dtype=dt, device=dev)
+            c = torch.zeros((size, size), dtype=torch.float32, device=dev)
+            g.fill_normal(a, sigma, SEED_BASE + 300)
+            g.fill_normal(b, sigma, SEED_BASE + 301)
+            torch.cuda.synchronize()
+            with torch.cuda.stream(torch.cuda.default_stream(dev)):      # the reference launches on the legacy default stream
+                ref_ms = protocol(lambda: fn(size, size, size, a.data_ptr(), b.data_ptr(), c.data_ptr()))
+                ours_ms = protocol(lambda: g.GEMM4(size, size, size, a, b, c))
+                best_ms = protocol(lambda: g.gemm_ex(a, b, c))
+            fl = 2.0 * size ** 3
+            out[f"{size}^3 {label}"] = {"reference_ms": ref_ms, "reference_tflops": fl / ref_ms / 1e9,
+                                        "ours_GEMM4_ms": ours_ms, "ours_GEMM4_tflops": fl / ours_ms / 1e9,
+                                        "ours_auto_depth_ms": best_ms, "ours_auto_depth_tflops": fl / best_ms / 1e9,
+                                        "speedup_GEMM4_over_reference": ref_ms / ours_ms}
+            del a, b, c
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_sparse(args, g, torch, dev, json_fd):
@@ -309,6 +625,55 @@ def run_sparse(args, g, torch, dev, json_fd):
     return 0
 
 
+def run_phase_timeline(args, g, torch, dev, json_fd, pkg):
+    """Where one launch of the M <= 128 kernels spends its time, from the kernels' own %globaltimer stamps.  Needs the
+    diagnostics build of the library (make -C tensor-core-fp8_b200/csrc diag; B200FP8_LIBRARY points at it and
+    B200FP8_DEBUG=1024 switches the stamps on): the product build has no such code."""
+    import numpy as np
+    lib = pkg._cabi.lib()
+    if not hasattr(lib, "b200fp8_debug_trace_copy"):
+        raise SystemExit("--phase-timeline needs the diagnostics build: B200FP8_LIBRARY=.../libb200fp8_diag.so B200FP8_DEBUG=1024")
+    lib.b200fp8_debug_trace_copy.argtypes = [ctypes.POINTER(ctypes.c_longlong), ctypes.c_int, ctypes.c_int]
+    M, K, N, _ = WORKLOADS[args.workload]
+    kernel = args.kernel or 4
+    names = {4: ["entry", "set-up done", "first block in shared memory", "accumulator complete", "epilogue woke",
+                 "first cluster barrier passed", "reduce-scatter + stores done", "end"],
+             8: ["entry", "grid dependency wait passed", "first block in shared memory", "MMA warp done",
+                 "finisher saw its peers' flags", "epilogue done", "end", ""]}.get(kernel)
+    if names is None or M > 128:
+        raise SystemExit("--phase-timeline covers the M <= 128 kernels (--kernel 4 or 8)")
+    f8 = torch.float8_e4m3fn
+    a = torch.empty((M, K), dtype=f8, device=dev)
+    g.fill_normal(a, 1.0, 1)
+    bs = [torch.empty((N, K), dtype=f8, device=dev) for _ in range(6)]
+    for i, b in enumerate(bs):
+        g.fill_normal(b, 1.0, 2 + i)
+    c = torch.empty((M, N), dtype=torch.float32, device=dev)
+    for i in range(3):
+        g.gemm_ex(a, bs[i], c, kernel=kernel)
+    torch.cuda.synchronize()
+    words = 3 * 4096
+    buf = (ctypes.c_longlong * words)()
+    lib.b200fp8_debug_trace_copy(buf, words, 1)
+    g.gemm_ex(a, bs[3], c, kernel=kernel)      # two launches back to back: the stamps kept are the second launch's,
+    g.gemm_ex(a, bs[4], c, kernel=kernel)      # which started under the first one's tail (dependent launch)
+    torch.cuda.synchronize()
+    nw = lib.b200fp8_debug_trace_copy(buf, words, 1)
+    t = np.array(buf[:nw], dtype=np.int64).reshape(-1, 8)
+    t = t[t[:, 0] > 0]
+    t0 = t[:, 0].min()
+    rows = {}
+    for i, nm in enumerate(names):
+        col = t[:, i][t[:, i] > 0]
+        if nm and len(col):
+            rows[nm] = {"median_us": float(np.median(col - t0)) / 1e3, "min_us": float(col.min() - t0) / 1e3,
+                        "max_us": float(col.max() - t0) / 1e3, "ctas": int(len(col))}
+    line = {"phase_timeline": rows, "config": {"workload": args.workload, "M": M, "K": K, "N": N, "kernel": kernel},
+            "ctas": int(len(t)), "unit": "microseconds after the first CTA's entry"}
+    os.write(json_fd, (json.dumps(line) + "\n").encode())
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -319,11 +684,10 @@ def main() -> int:
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extras", action="store_true", help="skip the cuBLASLt / 8192^3 side measurements")
-    ap.add_argument("--allgather", action="store_true", help="also time an NCCL all-gather of the C shards (N > 1)")
-    ap.add_argument("--fused-allgather", action="store_true",
-                    help="also time the GEMM with the all-gather fused into its epilogue (N > 1): every rank ends with all of C")
-    ap.add_argument("--multimem", action="store_true", help="fused all-gather through NVSwitch multicast (multimem stores)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the configs / reference-kernel / collective legs")
+    ap.add_argument("--no-parity", action="store_true", help="skip the check of the timed C buffer")
+    ap.add_argument("--multimem", action="store_true", help="fused all-gather through NVSwitch multicast only (multimem stores)")
+    ap.add_argument("--phase-timeline", action="store_true", help="kernel time stamps of one launch (diagnostics build)")
     ap.add_argument("--kernel", type=int, default=0)
     ap.add_argument("--depth", type=int, default=0)
     ap.add_argument("--a-dtype", default="e4m3", choices=["e4m3", "e5m2"])
@@ -340,6 +704,15 @@ def main() -> int:
     json_fd = os.dup(1)
     os.dup2(2, 1)
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        # the launcher exports OMP_NUM_THREADS=1; the parity checks run the FP64 oracle on the host, so every rank
+        # gets its share of the host threads instead (set before any OpenMP runtime is loaded)
+        os.environ["OMP_NUM_THREADS"] = str(max(1, host_threads() // world))
+
+    import datetime
     import torch
     import torch.distributed as dist
     from __graft_entry__ import load_package
@@ -347,9 +720,6 @@ def main() -> int:
     g = pkg.gemm
     shard_mod = pkg.shard
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     if not torch.cuda.is_available():
@@ -360,11 +730,13 @@ def main() -> int:
         if world > 1:
             raise SystemExit("the sparse workloads run on one GPU")
         return run_sparse(args, g, torch, dev, json_fd)
+    if args.phase_timeline:
+        return run_phase_timeline(args, g, torch, dev, json_fd, pkg)
     if world > 1:
         # keep stdout to the one JSON line: NCCL prints its version banner there at NCCL_DEBUG=VERSION
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
             os.environ["NCCL_DEBUG"] = "WARN"
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
 
     M, K, N, sharded = WORKLOADS[args.workload]
     sh = shard_mod.column_shard(N, rank, world) if sharded else shard_mod.Shard(rank, world, 0, N)
@@ -373,11 +745,10 @@ def main() -> int:
     f8_of = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
     fa, fb = f8_of[args.a_dtype], f8_of[args.b_dtype]
     sig_a, sig_b = (1.0 if args.a_dtype == "e4m3" else 2.0), (1.0 if args.b_dtype == "e4m3" else 2.0)
-    f8 = torch.float8_e4m3fn
+    peaks = measured_peaks()
 
     # operands: several B (and C) buffers for small workloads so that every step reads from HBM, not L2
-    bytes_per_set = n_local * K + 4 * M * n_local
-    nsets = 1 if (M * K + bytes_per_set) > (512 << 20) else max(2, min(8, (1 << 30) // max(1, bytes_per_set)))
+    nsets = operand_sets(M, K, n_local)
     a = torch.empty((M, K), dtype=fa, device=dev)
     g.fill_normal(a, sig_a, seed_a)
     bs, cs = [], []
@@ -397,12 +768,16 @@ def main() -> int:
             dist.barrier()
             torch.cuda.synchronize()
 
+    def max_over_ranks(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for i in range(args.warmup):
         step(i)
     barrier()
-    # Short steps are launch-bound when driven call by call from Python, so their K steps are captured
-    # once in a CUDA graph and replayed; long steps are timed launch by launch.
-    use_graph = 2.0 * M * K * n_local < 2e12
+    use_graph = graph_timed(M, K, n_local)
     launches0 = g.launch_count()
     if use_graph:
         graph = torch.cuda.CUDAGraph()
@@ -435,10 +810,7 @@ def main() -> int:
         per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     if g.device_status() != 0:
         raise SystemExit("device status word is non-zero: a kernel's bounded wait ran out")
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    max_ms = float(t.item())
+    max_ms = max_over_ranks(total_ms)
     ms_per_step = max_ms / args.steps
 
     replicas = 1 if sharded else world
@@ -446,7 +818,6 @@ def main() -> int:
     value = flops_job / (ms_per_step * 1e-3) / 1e12
 
     # roofline of the dominant kernel on this rank
-    peaks = measured_peaks()
     flops_launch = 2.0 * M * K * n_local
     bytes_launch = float(M * K + n_local * K + 4 * M * n_local)
     avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
@@ -458,9 +829,13 @@ def main() -> int:
                 "frac_of_nominal_8TBs": ach / NOMINAL_HBM_GBS}
     else:
         ach = flops_launch / (avg_launch_ms * 1e-3) / 1e12
-        peak = 2.0 * peaks["bf16_sustained"]
+        # a timed region of at least a few hundred milliseconds runs at the power cap: the sustained figure applies
+        sustained = total_ms >= 200.0
+        peak = 2.0 * (peaks["bf16_sustained"] if sustained else peaks["bf16_burst"])
         roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                "peak_source": peaks["source"] + ": 2 x sustained cuBLAS bf16 (fp8 issues at twice the bf16 rate)",
+                "peak_source": peaks["source"] + (": 2 x sustained cuBLAS bf16" if sustained else ": 2 x burst cuBLAS bf16 (timed region shorter than 0.2 s)")
+                               + " (fp8 issues at twice the bf16 rate)",
+                "frac_of_sustained_peak": ach / (2.0 * peaks["bf16_sustained"]),
                 "frac_of_burst_peak": ach / (2.0 * peaks["bf16_burst"]),
                 "frac_of_nominal_4500": ach / NOMINAL_FP8_TFLOPS}
     roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None   # captured at N = 1
@@ -472,36 +847,69 @@ def main() -> int:
         "metric": "fp8_gemm_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "n_per_rank": n_local, "layout": "row-col",
-                   "a": args.a_dtype, "b": args.b_dtype, "out": "f32", "parallelism": f"n-shard x{world}" if sharded else f"replicas x{world}",
-                   "l2": "inputs larger than L2" if nsets == 1 else f"rotating over {nsets} distinct B/C buffer sets larger than L2",
-                   "kernel": args.kernel, "depth": args.depth,
-                   "timing": "one CUDA graph of all steps, replayed" if use_graph else "launch by launch"},
+        "config": workload_config(args, M, K, N, n_local, world, sharded, describe_l2(nsets),
+                                  "one CUDA graph of all steps, replayed" if use_graph else "launch by launch"),
         "roofline": roof, "gpu_launches": int(launches), "clocks": clk.summary(),
         "pct_of_nominal_fp8_peak": 100.0 * value / (NOMINAL_FP8_TFLOPS * world),
     }
 
+    # ---- the buffer that was timed, checked (every rank checks its own block; the worst over ranks is reported) ----
+    if not args.no_parity:
+        p = parity_of(torch, g, a, bs[0], cs[0], rows=8 if world == 1 else 4, cols=8 if world == 1 else 4, points=4096 if world == 1 else 2048)
+        p["worst"] = max_over_ranks(p["worst"])
+        p["buffer"] = "C of the timed steps (every rank its own column block; worst over ranks)"
+        line["parity"] = p
+        if p["worst"] > 1.0:
+            raise SystemExit(f"the timed C buffer is outside the tolerance: {p}")
+
+    # ---- N > 1: a steady-state leg.  The counted steps above last a few milliseconds per rank at N = 8 and never reach
+    #      the power-capped clocks the N = 1 run sits at, so 1 -> N would compare two power regimes: here every rank runs
+    #      back to back for at least a second, and the per-GPU rate comes with the SM clock it was measured at ----
+    if world > 1 and not args.no_extras:
+        per = max(avg_launch_ms, 1e-3)
+        reps = int(min(2000, max(args.steps, 1100.0 / per)))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with ClockSampler(physical_gpu_index(local_rank)) as sclk:
+            e0.record()
+            for i in range(reps):
+                step(i)
+            e1.record()
+            torch.cuda.synchronize()
+        barrier()
+        sus_ms = max_over_ranks(e0.elapsed_time(e1)) / reps
+        mhz = sclk.summary()["sm_mhz"]
+        mhz_max = max_over_ranks(float(mhz or 0))
+        mhz_min = -max_over_ranks(-float(mhz or 0))
+        line["sustained"] = {"steps": reps, "ms_per_step": sus_ms, "tflops_per_gpu": flops_launch / sus_ms / 1e9,
+                             "tflops_job": flops_job / sus_ms / 1e9, "median_sm_mhz_rank0": mhz,
+                             "median_sm_mhz_over_ranks": [mhz_min, mhz_max], "reasons_rank0": sclk.summary()["reasons"],
+                             "ms_times_mhz_rank0": (sus_ms * mhz) if mhz else None,
+                             "frac_of_sustained_peak": flops_launch / sus_ms / 1e9 / (2.0 * peaks["bf16_sustained"]),
+                             "note": "max over ranks; compare with the N = 1 line's ms_per_step x clocks.sm_mhz"}
+
     # ---- end to end from pinned HOST buffers: uploads, operator and the download of C inside the timed region.
     #      N = 1: the C ABI's host-pointer entry point.  N > 1 (sharded): every rank uploads M/N rows of A and its
-    #      rows of B, A is all-gathered over NVLink, C blocks are downloaded while the next block computes. ----
+    #      rows of B, the rows of A go round over NVLink, C blocks are downloaded while the next block computes. ----
     if not args.no_e2e:
         hb = torch.empty((n_local, K), dtype=torch.uint8).pin_memory().view(fb)
         hc = torch.empty((M, n_local), dtype=torch.float32).pin_memory()
         hb.view(torch.uint8).copy_(bs[0].view(torch.uint8))
         sharded_e2e = world > 1 and sharded and M % world == 0
+        phases = None
         if sharded_e2e:
             rows = M // world
             ha = torch.empty((rows, K), dtype=torch.uint8).pin_memory().view(fa)
             ha.view(torch.uint8).copy_(a[rank * rows:(rank + 1) * rows].view(torch.uint8))
             runner = shard_mod.HostShardedGemm(M, K, sh, fa, fb, dev)
-            call = lambda: runner(ha, hb, hc, depth=args.depth, kernel=args.kernel)
-            api = ("shard.HostShardedGemm (upload M/N rows of A and the B shard; NCCL all-gather of A; operator in row "
-                   "blocks; download of C overlapped), wall clock, max over ranks")
+            call = lambda **kw: runner(ha, hb, hc, depth=args.depth, kernel=args.kernel, **kw)
+            api = ("shard.HostShardedGemm (upload M/N rows of A and the B shard; rows of A broadcast rank by rank over NVLink; "
+                   "operator in row blocks as the rows arrive; download of C overlapped), wall clock, max over ranks")
             h2d = rows * K + n_local * K
         else:
             ha = torch.empty((M, K), dtype=torch.uint8).pin_memory().view(fa)
             ha.view(torch.uint8).copy_(a.view(torch.uint8))
-            call = lambda: g.gemm_host(ha, hb, hc, depth=args.depth)
+            call = lambda **kw: g.gemm_host(ha, hb, hc, depth=args.depth)
             api = "b200fp8_gemm_rowcol_f32_host (upload A, B; operator; download C), wall clock, max over ranks"
             h2d = M * K + n_local * K
         call()                                                   # warm-up: allocates device buffers
@@ -510,159 +918,125 @@ def main() -> int:
         for _ in range(args.e2e_steps):
             call()
         e2e_ms = (time.perf_counter() - t0) * 1e3               # each call returns when C is in host memory
-        tt = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tt.item()) / args.e2e_steps
-        if sharded_e2e:                                          # the downloaded block must be the operator's result
-            if not torch.equal(hc[:4096].to(dev), cs[0][:4096]):
-                raise SystemExit("end-to-end result differs from the device-resident result")
+        e2e_ms = max_over_ranks(e2e_ms) / args.e2e_steps
+        if sharded_e2e:
+            barrier()
+            phases = call(breakdown=True)                        # one more call, with device time stamps per phase
+            phases = {k: max_over_ranks(v) for k, v in phases.items()}
+            barrier()
+        # the downloaded block must be the operator's result: bit for bit the device-resident C of the timed steps
+        same = bool(torch.equal(hc[:2048].to(dev), cs[0][:2048]) and torch.equal(hc[-2048:].to(dev), cs[0][-2048:]))
+        if not same:
+            raise SystemExit("end-to-end result differs from the device-resident result")
         line["e2e"] = {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
                        "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(4 * M * n_local),
-                       "ms_per_step": e2e_ms, "steps": args.e2e_steps, "api": api}
+                       "ms_per_step": e2e_ms, "steps": args.e2e_steps, "api": api,
+                       "parity": "first and last 2048 rows of the downloaded C equal the device-resident C of the timed steps bit for bit"}
+        if phases is not None:
+            line["e2e"]["phase_end_ms"] = phases
+            line["e2e"]["phase_note"] = "device time stamps of one more call, milliseconds after its start, max over ranks"
         del ha, hb, hc
+        if sharded_e2e:
+            del runner
+        if world == 1:
+            pkg._cabi.lib().b200fp8_host_release()
+        torch.cuda.empty_cache()
 
-    # ---- optional NCCL all-gather of the C shards, timed separately ----
-    if args.allgather and world > 1 and sharded:
+    # ---- N > 1: the all-gather of the C blocks, separately (NCCL) and fused into the GEMM's epilogue ----
+    if world > 1 and sharded and not args.no_extras:
+        recv_bytes = 4.0 * M * n_local * (world - 1)
         full = torch.empty((world, M, n_local), dtype=torch.float32, device=dev)
         dist.all_gather_into_tensor(full, cs[0])
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
         e0.record()
-        dist.all_gather_into_tensor(full, cs[0])
+        for _ in range(reps):
+            dist.all_gather_into_tensor(full, cs[0])
         e1.record()
         torch.cuda.synchronize()
-        tg = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
-        line["allgather"] = {"ms": float(tg.item()), "bytes_received_per_rank": int(4 * M * n_local * (world - 1)),
-                             "layout": "[rank][M][N/R] blocks"}
-        del full
-
-    # ---- the same step with the all-gather of C fused into the kernel's epilogue (peer stores over NVLink) ----
-    if args.fused_allgather and world > 1 and sharded:
-        shared = shard_mod.SharedC(M, N, dev, multicast=args.multimem)
-        fsteps = max(3, min(args.steps, 10))
-        for _ in range(2):
-            shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
+        ag_ms = max_over_ranks(e0.elapsed_time(e1) / reps)
+        own_ok = bool(torch.equal(full[rank], cs[0]))
+        line["allgather"] = {"ms": ag_ms, "bytes_received_per_rank": int(recv_bytes), "gbs_received_per_gpu": recv_bytes / ag_ms / 1e6,
+                             "frac_of_measured_nvlink": recv_bytes / ag_ms / 1e6 / NVLINK_PEER_COPY_GBS,
+                             "layout": "[rank][M][N/R] blocks (a re-layout pass would still be needed for row-major C)",
+                             "gemm_plus_allgather_ms": ms_per_step + ag_ms, "parity": {"own_block_bitwise": own_ok}}
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(fsteps):
-            shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
-        e1.record()
+        variants = [("fused_allgather_multimem", True)] if args.multimem else [("fused_allgather", False), ("fused_allgather_multimem", True)]
+        # reference for the parity of the gathered matrix: the unsharded operator on a row block, computed here
+        rb = 1024
+        b_full = torch.empty((N, K), dtype=fb, device=dev)
+        g.fill_normal(b_full, sig_b, seed_b)
+        want_rows = torch.empty((rb, N), dtype=torch.float32, device=dev)
+        g.gemm_ex(a[:rb], b_full, want_rows, depth=args.depth, kernel=args.kernel)
         torch.cuda.synchronize()
-        barrier()
-        tf = torch.tensor([e0.elapsed_time(e1) / fsteps], dtype=torch.float64, device=dev)
-        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
-        fms = float(tf.item())
-        line["fused_allgather"] = {"ms_per_step": fms, "tflops": 2.0 * M * K * N / (fms * 1e-3) / 1e12, "steps": fsteps,
-                                   "stores": "multimem (NVSwitch multicast)" if args.multimem else "unicast peer stores",
-                                   "nvlink_bytes_sent_per_rank": int(4 * M * n_local * (1 if args.multimem else world - 1)),
-                                   "result": "every rank holds the full row-major C; no separate collective, no re-layout"}
-        if g.device_status() != 0:
-            raise SystemExit("device status word is non-zero after the fused run")
-        shared.close()
-
-    # ---- side measurements on rank 0 at N = 1: the 8192^3 target shape and the bench workload, ours against
-    #      cuBLASLt on the same buffers, ALTERNATING so that both see the same clocks and temperature ----
-    if rank == 0 and world == 1 and not args.no_extras:
-        extras = {}
-        cmp_path = pkg._cabi.CMP_LIB_PATH
-        cmp = ctypes.CDLL(cmp_path) if os.path.exists(cmp_path) else None
-        ci, vp, fp = ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)
-        if cmp is not None:
-            cmp.b200fp8_cmp_cublaslt.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, ci, ci, fp, ctypes.POINTER(ci), vp]
-            cmp.b200fp8_cmp_cublaslt_run.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, fp, vp]
-        stream = torch.cuda.current_stream().cuda_stream
-        # a short workload goes first: after the power-capped 8192^3 runs the clocks need a while to recover
-        order = (args.workload, "gemm8192") if 2.0 * M * K * n_local < 2e12 else ("gemm8192", args.workload)
-        for name in order:
-            if name in extras:
-                continue
-            m2, k2, n2, _ = WORKLOADS[name]
-            if name == args.workload:
-                a2, b2, c2 = a, bs[0], cs[0]
-                n2 = n_local
-            else:
-                a2 = torch.empty((m2, k2), dtype=f8, device=dev)
-                b2 = torch.empty((n2, k2), dtype=f8, device=dev)
-                c2 = torch.empty((m2, n2), dtype=torch.float32, device=dev)
-                g.fill_normal(a2, 1.0, seed_a + 7)
-                g.fill_normal(b2, 1.0, seed_b + 7)
-            fl = 2.0 * m2 * k2 * n2
-            # every round: a lead-in that is not timed (the clocks settle to THIS kernel's steady state: a power-capped
-            # GPU carries the other kernel's clocks over the switch), then the timed launches
-            iters, lead = (20, 20) if fl < 5e12 else (6, 3)
-            have_cmp = False
-            if cmp is not None:
-                ms = ctypes.c_float(-1)
-                found = ci(0)
-                have_cmp = cmp.b200fp8_cmp_cublaslt(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), b2.data_ptr(), g.dtype_code(b2), c2.data_ptr(), 3, 8, 0,
-                                                    ctypes.byref(ms), ctypes.byref(found), stream) == 0
-            ours, theirs = [], []
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            # short kernels: both sides as CUDA graphs of `iters` launches (no launch gaps on either side) over the
-            # workload's rotating operand sets (every launch streams from HBM); long ones launch by launch
-            side_graph = their_graph = None
-            rot_b, rot_c = (bs, cs) if name == args.workload else ([b2], [c2])
-            if fl < 2e12:
-                for i in range(2):
-                    g.gemm_ex(a2, rot_b[i % len(rot_b)], rot_c[i % len(rot_c)], depth=args.depth, kernel=args.kernel)
-                torch.cuda.synchronize()
-                side_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(side_graph):
-                    for i in range(iters):
-                        g.gemm_ex(a2, rot_b[i % len(rot_b)], rot_c[i % len(rot_c)], depth=args.depth, kernel=args.kernel)
-                if have_cmp:
-                    cmp.b200fp8_cmp_cublaslt_enqueue.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp]
-                    their_graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(their_graph):
-                        cap = torch.cuda.current_stream().cuda_stream
-                        for i in range(iters):
-                            cmp.b200fp8_cmp_cublaslt_enqueue(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), rot_b[i % len(rot_b)].data_ptr(),
-                                                             g.dtype_code(b2), rot_c[i % len(rot_c)].data_ptr(), cap)
-
-            def ours_launches(count):
-                if side_graph is not None:
-                    side_graph.replay()                   # the graph holds `iters` (= lead) launches
-                else:
-                    for _ in range(count):
-                        g.gemm_ex(a2, b2, c2, depth=args.depth, kernel=args.kernel)
-
-            for rnd in range(4):
-                ours_launches(lead)
-                e0.record()
-                ours_launches(iters)
-                e1.record()
-                torch.cuda.synchronize()
-                if rnd:                                   # the first pass warms both up
-                    ours.append(e0.elapsed_time(e1) / iters)
-                if their_graph is not None:
-                    their_graph.replay()
+        for key, mc in variants:
+            shared = None
+            entry = {}
+            try:
+                try:
+                    shared = shard_mod.SharedC(M, N, dev, multicast=mc)
+                except RuntimeError as e:
+                    if mc and "multicast" in str(e):
+                        entry = {"unavailable": "no NVLink multicast for symmetric memory on this system"}
+                    else:
+                        raise
+                if shared is not None:
+                    shared.own.fill_(float("nan"))
+                    fsteps = max(3, min(args.steps, 10))
+                    for _ in range(2):
+                        shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
+                    barrier()
                     e0.record()
-                    their_graph.replay()
+                    for _ in range(fsteps):
+                        shard_mod.gemm_allgather(a, bs[0], shared, sh, N, depth=args.depth, kernel=args.kernel)
                     e1.record()
                     torch.cuda.synchronize()
-                    if rnd:
-                        theirs.append(e0.elapsed_time(e1) / iters)
-                elif have_cmp:
-                    ms = ctypes.c_float(-1)
-                    cmp.b200fp8_cmp_cublaslt_run(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), b2.data_ptr(), g.dtype_code(b2), c2.data_ptr(), lead,
-                                                 ctypes.byref(ms), stream)
-                    cmp.b200fp8_cmp_cublaslt_run(m2, k2, n2, a2.data_ptr(), g.dtype_code(a2), b2.data_ptr(), g.dtype_code(b2), c2.data_ptr(), iters,
-                                                 ctypes.byref(ms), stream)
-                    if rnd:
-                        theirs.append(ms.value)
-            o = sum(ours) / len(ours)
-            entry = {"ms": o, "tflops": fl / o / 1e9,
-                     "protocol": f"3 alternating rounds, each {lead} untimed lead-in launches then {iters} timed"
-                                 + ("; both sides as CUDA graphs" + (f" over {len(rot_b)} rotating operand sets" if len(rot_b) > 1 else "")
-                                    if side_graph is not None else "")}
-            if theirs:
-                t_ = sum(theirs) / len(theirs)
-                entry.update({"cublaslt_ms": t_, "cublaslt_tflops": fl / t_ / 1e9, "vs_cublaslt": t_ / o})
-            extras[name] = entry
-        line["side"] = extras
+                    barrier()
+                    fms = max_over_ranks(e0.elapsed_time(e1) / fsteps)
+                    status = g.device_status()
+                    # parity of the gathered matrix on THIS rank: a row block against the unsharded operator (bitwise),
+                    # and sampled points of the whole matrix against the FP64 oracle
+                    rows_equal = bool(torch.equal(shared.own[:rb], want_rows))
+                    import numpy as np
+                    from oracle import fp8_oracle as fo
+                    rng = np.random.default_rng(100 + rank)
+                    pm, pn = rng.integers(0, M, 1024), rng.integers(0, N, 1024)
+                    C64, S = fo.gemm_f64_points(a.view(torch.uint8).cpu().numpy(), g.dtype_code(a),
+                                                b_full.view(torch.uint8).cpu().numpy(), g.dtype_code(b_full), pm, pn)
+                    got = shared.own[torch.from_numpy(pm).to(dev), torch.from_numpy(pn).to(dev)].cpu().numpy()
+                    nbad, w, _ = fo.check_tolerance(got, C64, S)
+                    ok_all = max_over_ranks(0.0 if (rows_equal and nbad == 0 and status == 0) else 1.0) == 0.0
+                    sent = 4.0 * M * n_local * (1 if mc else world - 1)
+                    entry = {"ms_per_step": fms, "tflops": 2.0 * M * K * N / (fms * 1e-3) / 1e12, "steps": fsteps,
+                             "stores": "multimem (NVSwitch multicast)" if mc else "unicast peer stores",
+                             "nvlink_bytes_sent_per_rank": int(sent), "bytes_received_per_rank": int(recv_bytes),
+                             "gbs_received_per_gpu": recv_bytes / fms / 1e6,
+                             "frac_of_measured_nvlink": recv_bytes / fms / 1e6 / NVLINK_PEER_COPY_GBS,
+                             "roofline_ms": max(flops_launch / (2.0 * peaks["bf16_sustained"]) / 1e9, recv_bytes / NVLINK_PEER_COPY_GBS / 1e6),
+                             "vs_gemm_plus_nccl_allgather": (ms_per_step + ag_ms) / fms,
+                             "result": "every rank holds the full row-major C; no separate collective, no re-layout",
+                             "parity": {"rows_0_1023_bitwise_equal_unsharded_operator": rows_equal, "oracle_points": 1024,
+                                        "oracle_worst": max_over_ranks(float(w)), "device_status": status, "all_ranks_ok": ok_all}}
+            finally:
+                if shared is not None:
+                    shared.close()                               # collective; reached on every rank whatever happened above
+            line[key] = entry
+        del full, b_full, want_rows
+        torch.cuda.empty_cache()
+
+    # ---- N = 1, default workload: the other configurations and the comparator arms ----
+    if rank == 0 and world == 1 and not args.no_extras:
+        del a, bs, cs
+        torch.cuda.empty_cache()
+        cmp = Comparator(pkg._cabi.CMP_LIB_PATH)
+        if args.workload == "shard32768":
+            line["configs"], line["configs_summary"] = run_configs(torch, g, cmp, dev, peaks)
+        else:
+            code = {"e4m3": 0, "e5m2": 1}
+            line["configs"] = {args.workload: measure_config(torch, g, cmp, dev, args.workload, M, K, N, code[args.a_dtype],
+                                                             code[args.b_dtype], args.depth, args.kernel, peaks)}
+        line["side"] = {"reference_kernels": reference_kernels_side(torch, g, dev)}
 
     # ---- the reference's CPU loop timed on this box's host cores (rank 0, N = 1 only) ----
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

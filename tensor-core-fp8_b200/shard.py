@@ -168,12 +168,15 @@ def gemm_allgather(a, b_shard, shared: "SharedC", shard: Shard, n_total: int, *,
 class HostShardedGemm:
     """End to end from HOST buffers on R GPUs: what `b200fp8_gemm_rowcol_f32_host` does on one.
 
-    Uploading the replicated A once per rank would push R copies of it through the host's PCIe complex,
-    so every rank uploads only M/R rows of A (and its own rows of B) and the ranks all-gather A over
-    NVLink (NCCL, in place).  The operator then runs in row blocks whose C rows are downloaded while the
-    next block computes.  `__call__(a_rows_host, b_shard_host, c_shard_host)`: pinned host tensors holding
-    this rank's M/R rows of A, its rows of B and room for its M x n column block of C; returns when the
-    block is complete in host memory.
+    Uploading the replicated A once per rank would push R copies of it through the host's PCIe complex, so every
+    rank uploads only its M/R rows of A (and its own rows of B) and the ranks hand their rows to each other over
+    NVLink.  The phases overlap: uploads run on a copy stream; rank j's rows travel as broadcast j on a
+    communication stream; the operator runs in row blocks, the own block first (it needs no communication) and
+    block j as soon as broadcast j has landed; each finished block of C goes down on a third stream while the next
+    block computes.  `__call__(a_rows_host, b_shard_host, c_shard_host)`: pinned host tensors holding this rank's M/R
+    rows of A, its rows of B and room for its M x n column block of C; returns when the block is complete in host
+    memory.  With `breakdown=True` it also returns the milliseconds, from the call's start, at which each phase
+    ended on the device.
     """
 
     def __init__(self, m: int, k: int, shard: Shard, a_dtype, b_dtype, device, group=None, row_blocks: int = 8):
@@ -188,28 +191,69 @@ class HostShardedGemm:
         self.a = torch.empty((m, k), dtype=a_dtype, device=self.device)
         self.b = torch.empty((shard.n, k), dtype=b_dtype, device=self.device)
         self.c = torch.empty((m, shard.n), dtype=torch.float32, device=self.device)
-        step = -(-m // row_blocks)
+        # row blocks of the operator: every rank's rows of A in `sub` pieces, so that about `row_blocks` downloads overlap
+        sub = max(1, row_blocks // self.world)
+        step = -(-self.rows_own // sub)
         step = -(-step // 256) * 256
-        self.blocks = [(r0, min(m, r0 + step)) for r0 in range(0, m, step)]
+        self.blocks = {j: [(j * self.rows_own + r0, min((j + 1) * self.rows_own, j * self.rows_own + r0 + step))
+                           for r0 in range(0, self.rows_own, step)] for j in range(self.world)}
+        self.copy_in = torch.cuda.Stream(device=self.device)
+        self.comm = torch.cuda.Stream(device=self.device)
         self.copy_out = torch.cuda.Stream(device=self.device)
-        self.done = [torch.cuda.Event() for _ in self.blocks]
 
-    def __call__(self, a_rows_host, b_shard_host, c_shard_host, *, depth: int = 0, kernel: int = 0):
+    def __call__(self, a_rows_host, b_shard_host, c_shard_host, *, depth: int = 0, kernel: int = 0, breakdown: bool = False):
         import torch
         import torch.distributed as dist
         from . import gemm as g
+        ev = lambda: torch.cuda.Event(enable_timing=breakdown)
+        cur = torch.cuda.current_stream(self.device)
+        start, up_a, up_b, last_bcast, first_gemm, last_gemm, last_down = ev(), ev(), ev(), ev(), ev(), ev(), ev()
+        start.record(cur)
         r0 = self.rank * self.rows_own
         own = self.a[r0:r0 + self.rows_own]
-        own.view(torch.uint8).copy_(a_rows_host.view(torch.uint8), non_blocking=True)
-        self.b.view(torch.uint8).copy_(b_shard_host.view(torch.uint8), non_blocking=True)
+        self.copy_in.wait_stream(cur)
+        with torch.cuda.stream(self.copy_in):
+            own.view(torch.uint8).copy_(a_rows_host.view(torch.uint8), non_blocking=True)
+            up_a.record(self.copy_in)
+            self.b.view(torch.uint8).copy_(b_shard_host.view(torch.uint8), non_blocking=True)
+            up_b.record(self.copy_in)
+        arrived = {}
         if self.world > 1:
-            dist.all_gather_into_tensor(self.a.view(torch.uint8), own.view(torch.uint8), group=self.group)
-        cur = torch.cuda.current_stream(self.device)
-        for (lo, hi), ev in zip(self.blocks, self.done):
-            g.gemm_ex(self.a[lo:hi], self.b, self.c[lo:hi], depth=depth, kernel=kernel)
-            ev.record(cur)
-            self.copy_out.wait_event(ev)
-            with torch.cuda.stream(self.copy_out):
-                c_shard_host[lo:hi].copy_(self.c[lo:hi], non_blocking=True)
+            self.comm.wait_event(up_a)                       # rank j's broadcast sends rows that its upload wrote
+            with torch.cuda.stream(self.comm):
+                for j in range(self.world):                  # same order on every rank: broadcast j carries rank j's rows
+                    rows = self.a[j * self.rows_own:(j + 1) * self.rows_own]
+                    dist.broadcast(rows.view(torch.uint8), src=dist.get_global_rank(self.group, j) if self.group is not None else j,
+                                   group=self.group)
+                    arrived[j] = torch.cuda.Event()
+                    arrived[j].record(self.comm)
+                last_bcast.record(self.comm)
+        else:
+            last_bcast.record(cur)
+        cur.wait_event(up_a)
+        cur.wait_event(up_b)
+        order = [self.rank] + [j for j in range(self.world) if j != self.rank]
+        first = True
+        for j in order:
+            if j != self.rank:
+                cur.wait_event(arrived[j])
+            for (lo, hi) in self.blocks[j]:
+                g.gemm_ex(self.a[lo:hi], self.b, self.c[lo:hi], depth=depth, kernel=kernel)
+                done = torch.cuda.Event()
+                done.record(cur)
+                if first:
+                    first_gemm.record(cur)
+                    first = False
+                self.copy_out.wait_event(done)
+                with torch.cuda.stream(self.copy_out):
+                    c_shard_host[lo:hi].copy_(self.c[lo:hi], non_blocking=True)
+        last_gemm.record(cur)
+        last_down.record(self.copy_out)
         self.copy_out.synchronize()
+        self.comm.synchronize()
         cur.synchronize()
+        if not breakdown:
+            return None
+        return {"upload_a_rows": start.elapsed_time(up_a), "upload_b_shard": start.elapsed_time(up_b),
+                "a_rows_from_all_ranks": start.elapsed_time(last_bcast), "first_row_block_computed": start.elapsed_time(first_gemm),
+                "last_row_block_computed": start.elapsed_time(last_gemm), "last_c_block_in_host_memory": start.elapsed_time(last_down)}
