@@ -192,6 +192,44 @@ int b200fp8_gemm_rowcol_f32_allgather(int m, int k, int n_local, const void* a, 
                                       void* stream);
 
 /*
+ * The N-sharded GEMM over the GPUs of one box from ONE process: a plan object for C and C++
+ * callers (the reference's caller is a C++ program, GEMM/gemm_main.cpp:28-194; the reference
+ * itself is single-GPU, so these entry points have no counterpart to replace -- each shard
+ * runs the operator of GEMM/include/gemm.cuh:12-55 on its slab).
+ *
+ * Shard i of `num_shards` (<= 8) runs on CUDA device devices[i] and owns an even share of B's
+ * rows in units of 256 (rows [n_begin_i, n_end_i) of B = the same columns of C); A is
+ * replicated.  The compute step exchanges nothing.  Inside b200fp8_multi_run one host thread
+ * per shard enqueues `steps` operator calls on the shard's own stream, the threads start
+ * together, and *max_ms_per_step is the MAXIMUM over the shards of the device time per step.
+ * With `gather` != 0 every shard's C is the full M x N matrix and the kernels' epilogues
+ * store every finished box into all of them (b200fp8_gemm_rowcol_f32_allgather; peer access
+ * between the devices is enabled by b200fp8_multi_create; N must be a multiple of 4), so after
+ * the call every device holds the complete row-major C.  A device may appear more than once
+ * in `devices` (several shards on one GPU).
+ *
+ * b200fp8_multi_upload:      A (M x K) to every shard and B's slabs from HOST matrices (B is N x K).
+ * b200fp8_multi_fill_normal: the same operands generated on the devices (b200fp8_fill_normal;
+ *                            shard i generates exactly its slab of the full B).
+ * b200fp8_multi_download:    the row-major M x N result into c_host -- the column blocks of all
+ *                            shards, or with gather the full matrix of shard `from_shard`.
+ * b200fp8_multi_shard:       a shard's device, column range and DEVICE pointers (any out-pointer
+ *                            may be NULL); *ldc is C's row pitch in elements.
+ * b200fp8_multi_destroy:     waits for the shards' streams, then frees everything.
+ */
+typedef struct b200fp8_multi b200fp8_multi;
+int b200fp8_multi_create(int num_shards, const int* devices, int m, int k, int n, int a_dtype, int b_dtype, int gather,
+                         b200fp8_multi** plan);
+int b200fp8_multi_destroy(b200fp8_multi* plan);
+int b200fp8_multi_shard(const b200fp8_multi* plan, int shard, int* device, long long* n_begin, long long* n_end, void** a,
+                        void** b, float** c, long long* ldc);
+int b200fp8_multi_upload(b200fp8_multi* plan, const void* a_host, const void* b_host);
+int b200fp8_multi_fill_normal(b200fp8_multi* plan, float sigma_a, unsigned long long seed_a, float sigma_b,
+                              unsigned long long seed_b);
+int b200fp8_multi_run(b200fp8_multi* plan, int steps, const b200fp8_options* options, float* max_ms_per_step);
+int b200fp8_multi_download(b200fp8_multi* plan, float* c_host, int from_shard);
+
+/*
  * The whole call sequence of the reference's benchmark driver for one GEMM
  * (BmFN, GEMM/gemm_main.cpp:56-64 upload, :77 / :123 operator call, :161
  * download) with HOST pointers: uploads A and B, runs the operator, downloads

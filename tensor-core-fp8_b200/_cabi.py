@@ -39,6 +39,13 @@ DECLARED_SYMBOLS = (
     "b200fp8_gemm_rowcol_f32_host",
     "b200fp8_host_release",
     "b200fp8_gemm_rowcol_f32_noalloc",
+    "b200fp8_multi_create",
+    "b200fp8_multi_destroy",
+    "b200fp8_multi_shard",
+    "b200fp8_multi_upload",
+    "b200fp8_multi_fill_normal",
+    "b200fp8_multi_run",
+    "b200fp8_multi_download",
     "b200fp8_fill_normal",
     "b200fp8_device_status",
     "b200fp8_enable_peer_access",
@@ -108,6 +115,15 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_gemm_rowcol_f32_host.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci]
         L.b200fp8_gemm_rowcol_f32_noalloc.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, vp, vp]
         L.b200fp8_fill_normal.argtypes = [vp, ll, ci, ctypes.c_float, ull, ull, vp]
+        L.b200fp8_multi_create.argtypes = [ci, ctypes.POINTER(ci), ci, ci, ci, ci, ci, ci, ctypes.POINTER(vp)]
+        L.b200fp8_multi_destroy.argtypes = [vp]
+        L.b200fp8_multi_shard.argtypes = [vp, ci, ctypes.POINTER(ci), ctypes.POINTER(ll), ctypes.POINTER(ll), ctypes.POINTER(vp),
+                                          ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(ll)]
+        L.b200fp8_multi_upload.argtypes = [vp, vp, vp]
+        L.b200fp8_multi_fill_normal.argtypes = [vp, ctypes.c_float, ull, ctypes.c_float, ull]
+        L.b200fp8_multi_run.argtypes = [vp, ci, ctypes.POINTER(Options), ctypes.POINTER(ctypes.c_float)]
+        L.b200fp8_multi_download.argtypes = [vp, vp, ci]
+        L.b200fp8_host_release.argtypes = []
         L.b200fp8_enable_peer_access.argtypes = [ci]
         L.b200fp8_ipc_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
         L.b200fp8_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]

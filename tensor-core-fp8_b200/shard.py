@@ -257,3 +257,70 @@ class HostShardedGemm:
         return {"upload_a_rows": start.elapsed_time(up_a), "upload_b_shard": start.elapsed_time(up_b),
                 "a_rows_from_all_ranks": start.elapsed_time(last_bcast), "first_row_block_computed": start.elapsed_time(first_gemm),
                 "last_row_block_computed": start.elapsed_time(last_gemm), "last_c_block_in_host_memory": start.elapsed_time(last_down)}
+
+
+class MultiGpuPlan:
+    """The N-sharded GEMM over several GPUs from ONE process: a thin caller of the C ABI's `b200fp8_multi_*` plan,
+    which owns the shards' buffers, their streams and one host thread per shard.  `devices` lists the CUDA device of
+    every shard (a device may repeat: several shards on one GPU).  With `gather` the kernels' epilogues leave the full
+    row-major C on every device."""
+
+    def __init__(self, devices, m: int, k: int, n: int, a_dtype: int = 0, b_dtype: int = 0, gather: bool = False):
+        import ctypes
+        from . import _cabi
+        self._lib, self._ct = _cabi.lib(), ctypes
+        self.m, self.k, self.n, self.world, self.gather = m, k, n, len(devices), bool(gather)
+        arr = (ctypes.c_int * len(devices))(*devices)
+        self._plan = ctypes.c_void_p()
+        _cabi.check(self._lib.b200fp8_multi_create(len(devices), arr, m, k, n, a_dtype, b_dtype, 1 if gather else 0,
+                                                   ctypes.byref(self._plan)), "multi_create")
+
+    def shard(self, i: int):
+        """(device, n_begin, n_end, a_ptr, b_ptr, c_ptr, ldc) of shard i; the pointers are device addresses."""
+        ct = self._ct
+        dev, nb, ne, ldc = ct.c_int(), ct.c_longlong(), ct.c_longlong(), ct.c_longlong()
+        a, b, c = ct.c_void_p(), ct.c_void_p(), ct.c_void_p()
+        from . import _cabi
+        _cabi.check(self._lib.b200fp8_multi_shard(self._plan, i, ct.byref(dev), ct.byref(nb), ct.byref(ne), ct.byref(a), ct.byref(b),
+                                                  ct.byref(c), ct.byref(ldc)), "multi_shard")
+        return dev.value, nb.value, ne.value, a.value, b.value, c.value, ldc.value
+
+    def upload(self, a_host, b_host):
+        from . import _cabi
+        shapes_ok = tuple(a_host.shape) == (self.m, self.k) and tuple(b_host.shape) == (self.n, self.k)
+        if a_host.is_cuda or b_host.is_cuda or not shapes_ok or not (a_host.is_contiguous() and b_host.is_contiguous()):
+            raise ValueError("upload takes contiguous HOST matrices a [M][K] and b [N][K]")
+        _cabi.check(self._lib.b200fp8_multi_upload(self._plan, a_host.data_ptr(), b_host.data_ptr()), "multi_upload")
+
+    def fill_normal(self, sigma_a: float, seed_a: int, sigma_b: float, seed_b: int):
+        from . import _cabi
+        _cabi.check(self._lib.b200fp8_multi_fill_normal(self._plan, float(sigma_a), int(seed_a), float(sigma_b), int(seed_b)),
+                    "multi_fill_normal")
+
+    def run(self, steps: int = 1, *, depth: int = 0, kernel: int = 0) -> float:
+        """`steps` operator calls per shard, all shards at once; returns the maximum over the shards of ms per step."""
+        from . import _cabi
+        ct = self._ct
+        opt = _cabi.Options(ct.sizeof(_cabi.Options), depth, kernel, 0, 0)
+        ms = ct.c_float(0)
+        _cabi.check(self._lib.b200fp8_multi_run(self._plan, steps, ct.byref(opt), ct.byref(ms)), "multi_run")
+        return ms.value
+
+    def download(self, c_host, from_shard: int = 0):
+        import torch
+        from . import _cabi
+        if c_host.is_cuda or c_host.dtype != torch.float32 or tuple(c_host.shape) != (self.m, self.n) or not c_host.is_contiguous():
+            raise ValueError("download takes a contiguous HOST float32 matrix [M][N]")
+        _cabi.check(self._lib.b200fp8_multi_download(self._plan, c_host.data_ptr(), from_shard), "multi_download")
+        return c_host
+
+    def close(self):
+        if self._plan:
+            self._lib.b200fp8_multi_destroy(self._plan)
+            self._plan = self._ct.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
