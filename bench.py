@@ -639,7 +639,7 @@ def run_phase_timeline(args, g, torch, dev, json_fd, pkg):
     names = {4: ["entry", "set-up done", "first block in shared memory", "accumulator complete", "epilogue woke",
                  "first cluster barrier passed", "reduce-scatter + stores done", "end"],
              8: ["entry", "grid dependency wait passed", "first block in shared memory", "MMA warp done",
-                 "finisher saw its peers' flags", "epilogue done", "end", ""]}.get(kernel)
+                 "finisher saw its peers' flags", "finisher's first bulk copy landed", "epilogue done", "end"]}.get(kernel)
     if names is None or M > 128:
         raise SystemExit("--phase-timeline covers the M <= 128 kernels (--kernel 4 or 8)")
     f8 = torch.float8_e4m3fn

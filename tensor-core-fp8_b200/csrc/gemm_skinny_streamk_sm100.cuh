@@ -407,6 +407,7 @@ gemm_fp8_skinny_streamk_kernel(const __grid_constant__ CUtensorMap tmap_b,   // 
                     fix_phase ^= 1u;
                     if (!landed) record_failure(args.status, abort_flag, kStatusSkinnyTimeout);
                     if (ptx::epilogue_any(!landed)) { fix_ok = false; break; }
+                    if (trace && half == 0 && tid == 0) trace[5] = static_cast<long long>(ptx::globaltimer_ns());
                 }
 #pragma unroll
                 for (int ch = 0; ch < L::kParkRows / 16; ++ch) {
@@ -472,7 +473,7 @@ gemm_fp8_skinny_streamk_kernel(const __grid_constant__ CUtensorMap tmap_b,   // 
         }
         __syncwarp();
         if (args.epi.amax != nullptr) amax_merge_warp(args.epi.amax, epi_amax);
-        if (trace && tid == 0) trace[5] = static_cast<long long>(ptx::globaltimer_ns());
+        if (trace && tid == 0) trace[6] = static_cast<long long>(ptx::globaltimer_ns());
     }
 
     ptx::tc_fence_before();
@@ -481,7 +482,7 @@ gemm_fp8_skinny_streamk_kernel(const __grid_constant__ CUtensorMap tmap_b,   // 
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem_base, L::kTmemCols);
     }
-    if (trace && threadIdx.x == 0) trace[6] = static_cast<long long>(ptx::globaltimer_ns());
+    if (trace && threadIdx.x == 0) trace[7] = static_cast<long long>(ptx::globaltimer_ns());
 }
 
 // Scratch memory of the stream-K kernel on one device: a ring of slots, one per launch in flight.  Each slot
