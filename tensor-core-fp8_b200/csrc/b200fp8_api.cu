@@ -103,9 +103,15 @@ cudaError_t encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes
     const cuuint64_t strides[1] = {ld * static_cast<uint64_t>(elem_bytes)};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
+    // L2 promotion of the copies: 256 bytes measured best or equal everywhere (B200FP8_L2_PROMOTION=0..3: none/64/128/256)
+    static const CUtensorMapL2promotion promo = [] {
+        const char* v = getenv("B200FP8_L2_PROMOTION");
+        const int p = v ? atoi(v) : 3;
+        return p == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : p == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+             : p == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    }();
     CUresult r = g_encode(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     cache.key[slot] = key; cache.map[slot] = *map; cache.used[slot] = true;
     return cudaSuccess;

@@ -26,7 +26,11 @@ namespace b200fp8 {
 
 constexpr int kSkinnyMaxM = 128;
 constexpr int kSkinnyTileN = 128;
-constexpr int kSkinnyThreads = 192;
+constexpr int kSkinnyThreads = 192;       // producer warp, MMA warp, four epilogue warps
+// For M > 32 the reduce-scatter moves 16-64 KiB per CTA through distributed shared memory, and a warp's remote loads
+// do not overlap each other (about half a microsecond per round): the CTA is launched with extra warps that do
+// nothing but help with that phase.
+constexpr int kSkinnyThreadsWide = 512;
 constexpr int kSkinnyMaxSplits = 8;      // portable cluster size
 
 struct SkinnyArgs {
@@ -88,8 +92,8 @@ __device__ __forceinline__ float4 ld_local_f4(uint32_t addr) {
     return v;
 }
 
-template <int MP>
-__global__ void __launch_bounds__(kSkinnyThreads, 2)
+template <int MP, int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS <= kSkinnyThreads ? 2 : 1)
 gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K], box 128 rows
                        const __grid_constant__ CUtensorMap tmap_a,   // A[M][K], box MP rows
                        const SkinnyArgs args)
@@ -135,9 +139,14 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         if (ptx::elect_one()) {
             const int first = blockIdx.y * args.kb_per_split;
             const int last = min(args.kb_total, first + min(args.kb_per_split, args.l2_prefetch));
-            for (int kb = first; kb < last; ++kb)
+            for (int kb = first; kb < last; ++kb) {
                 asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
                              ::"l"(reinterpret_cast<uint64_t>(&tmap_b)), "r"(kb * kBlockK), "r"(static_cast<int>(blockIdx.x) * kSkinnyTileN) : "memory");
+                // A is the same for every N tile: a few CTAs request it for all (it was evicted if B is larger than L2)
+                if (blockIdx.x < 2)
+                    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+                                 ::"l"(reinterpret_cast<uint64_t>(&tmap_a)), "r"(kb * kBlockK), "r"(0) : "memory");
+            }
         }
         __syncwarp();
     }
@@ -239,7 +248,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         if (ok && ptx::elect_one()) ptx::umma_commit(bar_acc);
         __syncwarp();
         if (trace && lane == 0) trace[3] = static_cast<long long>(ptx::globaltimer_ns());
-    } else {
+    } else if (warp < kSkinnyThreads / 32) {
         // ---------------- epilogue: 128 threads, thread = one column n of C ----------------
         // bar_acc completes after every MMA of this CTA has finished, i.e. after the ring's
         // shared memory was last read and long after it was last written: it is free to reuse.
@@ -282,7 +291,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
         const int m_end = min(args.M, m_begin + rows_per);
         const int items = max(0, m_end - m_begin) * (kSkinnyTileN / 4);      // float4 groups
         if (*abort_flag == 0) {
-            for (int i = threadIdx.x; i < items; i += kSkinnyThreads) {
+            for (int i = threadIdx.x; i < items; i += THREADS) {
                 const int m = m_begin + i / (kSkinnyTileN / 4);
                 const int cg = i % (kSkinnyTileN / 4);
                 const uint32_t local = smem_base + static_cast<uint32_t>((m * kSkinnyTileN + cg * 4) * 4);
@@ -384,11 +393,11 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
     *stages = st;
 }
 
-template <int MP>
+template <int MP, int THREADS>
 cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const SkinnyArgs& args, int n_tiles,
                              cudaStream_t stream) {
     using L = SkinnySmem<MP>;
-    auto kernel = gemm_fp8_skinny_kernel<MP>;
+    auto kernel = gemm_fp8_skinny_kernel<MP, THREADS>;
     static int attr_bytes[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -400,7 +409,7 @@ cudaError_t launch_skinny_mp(const CUtensorMap& tb, const CUtensorMap& ta, const
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(n_tiles), static_cast<unsigned>(args.splits), 1);
-    cfg.blockDim = dim3(kSkinnyThreads, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
     cfg.dynamicSmemBytes = static_cast<size_t>(bytes);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -448,11 +457,22 @@ inline cudaError_t launch_skinny(int sm_count, int* status, SkinnyEncodeFn enc, 
     cudaError_t e;
     if ((e = skinny_encode(enc, &tb, b, k, n, ldb, kSkinnyTileN)) != cudaSuccess) return e;
     if ((e = skinny_encode(enc, &ta, a, ell_col_ind ? ell_k_small : k, m, lda, mp)) != cudaSuccess) return e;
+    static const int threads_env = [] { const char* v = getenv("B200FP8_SKINNY_THREADS"); return v ? atoi(v) : 0; }();
+    // the wide launch needs the SM to itself (one CTA per SM) and only pays when there is something to exchange
+    const bool one_per_sm = static_cast<long long>(n_tiles) * args.splits <= sm_count;
+    int threads = (mp >= 64 && args.splits > 1 && one_per_sm) ? kSkinnyThreadsWide : kSkinnyThreads;
+    if (threads_env == 192 || (threads_env == 512 && one_per_sm) || (threads_env == 1024 && one_per_sm)) threads = threads_env;
     switch (mp) {
-        case 16: return launch_skinny_mp<16>(tb, ta, args, n_tiles, stream);
-        case 32: return launch_skinny_mp<32>(tb, ta, args, n_tiles, stream);
-        case 64: return launch_skinny_mp<64>(tb, ta, args, n_tiles, stream);
-        default: return launch_skinny_mp<128>(tb, ta, args, n_tiles, stream);
+        case 16: return launch_skinny_mp<16, kSkinnyThreads>(tb, ta, args, n_tiles, stream);
+        case 32: return launch_skinny_mp<32, kSkinnyThreads>(tb, ta, args, n_tiles, stream);
+        case 64:
+            if (threads == 1024) return launch_skinny_mp<64, 1024>(tb, ta, args, n_tiles, stream);
+            if (threads == 512) return launch_skinny_mp<64, 512>(tb, ta, args, n_tiles, stream);
+            return launch_skinny_mp<64, kSkinnyThreads>(tb, ta, args, n_tiles, stream);
+        default:
+            if (threads == 1024) return launch_skinny_mp<128, 1024>(tb, ta, args, n_tiles, stream);
+            if (threads == 512) return launch_skinny_mp<128, 512>(tb, ta, args, n_tiles, stream);
+            return launch_skinny_mp<128, kSkinnyThreads>(tb, ta, args, n_tiles, stream);
     }
 }
 
