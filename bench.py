@@ -55,6 +55,8 @@ WORKLOADS = {
     "skinny64": (64, 8192, 8192, False),
     "skinny128": (128, 8192, 8192, False),
     "skinny_wide": (32, 8192, 57344, False),
+    "m256": (256, 8192, 8192, False),
+    "m512": (512, 8192, 8192, False),
 }
 # Sparse workloads (blocked-ELL A, 128 x 128 blocks; one GPU): name -> (op, M, K, N, stored blocks per block row)
 SPARSE_WORKLOADS = {

@@ -21,8 +21,6 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kPaceSlots = 256;
-constexpr int kSplitSlots = 64;          // split-K flag regions, one per launch in flight
-constexpr int kSplitSlotWords = 1024;    // flags per region: tiles x CTAs per tile x epilogue warps
 
 struct DeviceCtx {
     bool ready = false;
@@ -30,8 +28,6 @@ struct DeviceCtx {
     int* status = nullptr;          // device status word
     unsigned int* pace = nullptr;   // ring of tile-pacing counters, one per launch in flight
     unsigned int pace_next = 0;
-    unsigned int* split_flags = nullptr;   // ring of split-K flag regions (zero between launches)
-    unsigned int split_next = 0;
     // buffers of the host-pointer entry point
     void* host_a = nullptr; size_t host_a_bytes = 0;
     void* host_b = nullptr; size_t host_b_bytes = 0;
@@ -77,8 +73,6 @@ cudaError_t get_ctx(DeviceCtx** out) {
         if ((e = cudaMalloc(&c.status, sizeof(int))) != cudaSuccess) return e;
         if ((e = cudaMemset(c.status, 0, sizeof(int))) != cudaSuccess) return e;
         if ((e = cudaMalloc(&c.pace, kPaceSlots * sizeof(unsigned int))) != cudaSuccess) return e;
-        if ((e = cudaMalloc(&c.split_flags, kSplitSlots * kSplitSlotWords * sizeof(unsigned int))) != cudaSuccess) return e;
-        if ((e = cudaMemset(c.split_flags, 0, kSplitSlots * kSplitSlotWords * sizeof(unsigned int))) != cudaSuccess) return e;
         c.ready = true;
     }
     *out = &c;
@@ -142,12 +136,10 @@ struct Tune {
     int split_tail = 1;
     int l2_loads = 0, l2_stores = 0;   // L2 eviction hints of operand loads / C stores (see GemmArgs)
     int pdl = 1;                  // launch with programmatic stream serialization (set-up overlaps the previous kernel's tail)
-    int split_k = 1;              // automatic two-way split of K over CTA pairs for problems of few tiles (0 = never)
     int host_block_m = 4096;      // host-pointer entry: edge of the C blocks it pipelines over (rows / columns)
     int host_block_n = 4096;
     Tune() {
         if (const char* v = getenv("B200FP8_PDL")) pdl = atoi(v);
-        if (const char* v = getenv("B200FP8_SPLIT_K")) split_k = atoi(v);
         if (const char* v = getenv("B200FP8_L2_LOADS")) l2_loads = atoi(v);
         if (const char* v = getenv("B200FP8_L2_STORES")) l2_stores = atoi(v);
         if (const char* v = getenv("B200FP8_HOST_BLOCK_M")) host_block_m = atoi(v) >= 256 ? atoi(v) : host_block_m;
@@ -202,8 +194,7 @@ struct EllSpec {
 template <int BN, int STAGES, int CTAS, int NACC>
 cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
-                        const PeerSet* peers, const Epilogue* epi, cudaStream_t stream, const EllSpec* ell = nullptr,
-                        int k_splits = 1) {
+                        const PeerSet* peers, const Epilogue* epi, cudaStream_t stream, const EllSpec* ell = nullptr) {
     using L = GemmSmem<BN, STAGES, CTAS, NACC>;
     static bool attr_done[kMaxDevices] = {};
     if (ell && CTAS != 1) return cudaErrorInvalidValue;       // a block row is one 128-row M-tile
@@ -280,29 +271,14 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     const bool split_tail = NACC == 1 && BN == 256 && tune().split_tail && tiles > units && rem > 0 && 2 * rem <= units;
     args.split_tiles = split_tail ? rem : 0;
     args.full_items = static_cast<int>(tiles) - args.split_tiles;
-    // two-way split of K: only the plain FP32 operator with TMA-writable C (the second half is added by TMA reductions)
-    args.k_splits = 1;
-    if (k_splits == 2 && !epi && !ell && args.tma_store && !(peers && (peers->count > 0 || peers->multicast)) &&
-        args.num_k_blocks >= 2 && tiles * CTAS * kEpiWarps <= kSplitSlotWords) {
-        args.k_splits = 2;
-        args.split_tiles = 0;
-        args.full_items = static_cast<int>(tiles);
-        {
-            std::lock_guard<std::mutex> lock(g_mutex);
-            args.split_flags = ctx.split_flags + static_cast<size_t>(ctx.split_next++ % kSplitSlots) * kSplitSlotWords;
-        }
-        units = ctx.sm_count / CTAS;
-        if (max_ctas > 0 && max_ctas / CTAS < units) units = max_ctas / CTAS > 0 ? max_ctas / CTAS : 1;
-        if (2 * tiles < units) units = static_cast<int>(2 * tiles);
-    }
     args.idesc_half = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN / 2);
     CUtensorMap tbh = tb;
-    if (split_tail && args.k_splits == 1 &&
+    if (split_tail &&
         (e = encode_2d(&tbh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows / 2)) != cudaSuccess)
         return e;
 
     // tile pacing for long persistent runs (pairs only): a fresh zeroed counter per launch, stream-ordered
-    if (CTAS == 2 && args.k_splits == 1 && tune().pace_min_waves > 0 && tiles >= static_cast<long long>(tune().pace_min_waves) * units) {
+    if (CTAS == 2 && tune().pace_min_waves > 0 && tiles >= static_cast<long long>(tune().pace_min_waves) * units) {
         unsigned int* slot;
         {
             std::lock_guard<std::mutex> lock(g_mutex);
@@ -363,10 +339,6 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     cudaError_t e = get_ctx(&ctx);
     if (e != cudaSuccess) return e;
 
-    // K split over two CTA pairs for the tile kernels: options->split_k 2 forces it, 1 forbids it, 0 lets the rule below decide
-    int tile_splits = (split_k == 2 && kernel != B200FP8_KERNEL_AUTO && kernel != B200FP8_KERNEL_SKINNY &&
-                       kernel != B200FP8_KERNEL_SKINNY_STREAMK) ? 2 : 1;
-    const bool plain = !epi && !ell && !(peers && (peers->count > 0 || peers->multicast));
     if (kernel == B200FP8_KERNEL_AUTO) {
         const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
         const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
@@ -382,14 +354,6 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // long runs are power-limited: the wide tile moves a quarter less data per flop
         else if (wide_tiles >= 16LL * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N512;
         else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
-        // so few 256 x 256 tiles that twice as many work items still fit in one round, and a long K: every tile's K range
-        // is split over two pairs.  The alternative is more, smaller tiles, which move more operand bytes per flop than
-        // the L2 -> SM path delivers (M = 256, N = K = 8192: 96 bytes per SM clock wanted by 256 x 128 tiles, 64 by these)
-        else if (plain && tune().split_k && split_k != 1 && 2 * pair_tiles <= ctx->sm_count / 2 && k >= 4096 &&
-                 (((ldc * 4) % 16) == 0 && (n % 4) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0)) {
-            kernel = B200FP8_KERNEL_PAIR_N256;
-            tile_splits = 2;
-        }
         // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
         // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
         else if (4 * pair_tiles >= 3 * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N256;
@@ -411,7 +375,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
 
 #define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
 #define B200FP8_LAUNCH4(BN, ST, CT, NA) \
-    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell, tile_splits)
+    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
             return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);

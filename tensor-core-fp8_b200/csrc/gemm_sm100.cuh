@@ -131,13 +131,6 @@ struct GemmArgs {
     int full_items;       // number of full-width work items (= tiles - split_tiles)
     int split_tiles;      // tiles handled as two halves each (0 = off)
     uint32_t idesc_half;  // instruction descriptor for N = BN / 2
-    // Split-K over two CTA pairs (k_splits == 2, plain FP32 operator only): work item t < tiles is the first half of
-    // tile t's K range, item tiles + t the second half, on another pair at the same time.  The first half's pair
-    // stores its partial tile to C and raises one flag per epilogue warp; the second half's pair waits for the flag of
-    // the same warp position and then ADDS its partial tile into C with TMA reductions (FP32 add in L2).  Two terms,
-    // so the sum does not depend on arrival order; no workspace.  The consumer clears the flag it waited for.
-    int k_splits;         // 1 or 2
-    unsigned int* split_flags;   // [tiles][CTAS][kEpiWarps], zero at launch and left zero
     int l2_loads;         // L2 eviction hint of the operand loads: 0 none, 1 evict_last, 2 evict_first
     int l2_stores;        // ... of the FP32 TMA stores of C: 0 none, 2 evict_first
     int tma_store;        // 1: TMA-store epilogue (needs ldc % 4 == 0 and 16-byte aligned C); 0: plain stores
@@ -298,25 +291,13 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::griddep_launch_dependents();
 
     // persistent walk over work items, identical in every role
-    const int num_items = args.k_splits > 1 ? args.k_splits * args.full_items : args.full_items + 2 * args.split_tiles;
+    const int num_items = args.full_items + 2 * args.split_tiles;
     const int first_tile = blockIdx.x / CTAS;
     const int tile_step = gridDim.x / CTAS;
     const int nkb = args.num_k_blocks;
 
-    // split-K: item -> (tile, which half of K); everything else sees the tile index only
-    const int split_tiles_total = args.m_tiles * args.n_tiles;
-    auto split_of = [&](int t) { return (args.k_splits > 1 && t >= split_tiles_total) ? 1 : 0; };
-    auto kb_range = [&](int t, int& kb_begin, int& kb_end) {
-        kb_begin = 0;
-        kb_end = nkb;
-        if (args.k_splits > 1) {
-            const int mid = (nkb + 1) >> 1;
-            if (split_of(t)) kb_begin = mid; else kb_end = mid;
-        }
-    };
     // work item -> first row / column of this CTA's part; `half` = half-width tail item
     auto tile_coords = [&](int t, int& m0, int& n0, bool& half) {
-        if (args.k_splits > 1 && t >= split_tiles_total) t -= split_tiles_total;
         half = t >= args.full_items;
         int tile = t, h = 0;
         if (half) {
@@ -376,9 +357,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 ell_row = args.ell_col_ind + static_cast<long long>(m0 / kTileM) * nkb;
                 if (lane < nkb) ell_nxt = ell_row[lane];
             }
-            int kb_begin, kb_end;
-            kb_range(t, kb_begin, kb_end);
-            for (int kb = kb_begin; kb < kb_end; ++kb) {
+            for (int kb = 0; kb < nkb; ++kb) {
                 if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusProducerTimeout);
                     ok = false;
@@ -459,9 +438,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             int it = 0;
             bool ok = true;
             for (int t = first_tile; t < num_items && ok; t += tile_step, ++it) {
-                const uint32_t idesc = (args.k_splits == 1 && t >= args.full_items) ? args.idesc_half : args.idesc;
-                int kb_begin, kb_end;
-                kb_range(t, kb_begin, kb_end);
+                const uint32_t idesc = (t >= args.full_items) ? args.idesc_half : args.idesc;
                 // slot 0 of this tile must have been drained; slot 1 (NACC == 2) is awaited just before its first MMA
                 if (!wait_bounded(bar_tempty + 8 * slot_of(it, 0), use_parity(it) ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusMmaTimeout);
@@ -469,7 +446,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 ptx::tc_fence_after();
                 if (kDiagnostics && (args.debug & 128) && lane == 0 && it < 128) args.trace[(blockIdx.x / CTAS) * 128 + it] = static_cast<long long>(ptx::globaltimer_ns());
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                for (int kb = 0; kb < nkb; ++kb) {
                     long long tr0 = 0, tr1 = 0;
                     if (kDiagnostics && (args.debug & 64) && blockIdx.x == 0) tr0 = clock64();
                     if (!wait_bounded(bar_full + 8 * s, ph, abort_flag, pair, args.wait_hint_ns)) {
@@ -483,7 +460,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const uint64_t adesc = ptx::umma_desc_k128(a_src);
 #pragma unroll
                     for (int j = 0; j < NACC; ++j) {
-                        if (NACC == 2 && j == 1 && kb == kb_begin) {
+                        if (NACC == 2 && j == 1 && kb == 0) {
                             if (!wait_bounded(bar_tempty + 8, use_parity(it) ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                                 record_failure(args.status, abort_flag, kStatusMmaTimeout);
                                 ok = false;
@@ -496,7 +473,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         if (ptx::elect_one()) {
 #pragma unroll
                             for (int k = 0; k < kBlockK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
-                                if (!(kDiagnostics && (args.debug & 4))) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb_begin || k != 0);
+                                if (!(kDiagnostics && (args.debug & 4))) ptx::umma_f8<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
                         }
                         __syncwarp();
                     }
@@ -555,36 +532,6 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN + c_first * 32;
             const int col_base = n0 + (NACC == 2 ? grp * BN : 0) + c_first * 32;
-            // split-K: this warp's flag of the tile (same warp position in the pair that holds the other half of K)
-            unsigned int* split_flag = nullptr;
-            bool reduce_mode = false, skip_stores = false;
-            if (args.k_splits > 1) {
-                const int tile_idx = t - (split_of(t) ? split_tiles_total : 0);
-                split_flag = args.split_flags + (static_cast<long long>(tile_idx) * CTAS + rank) * kEpiWarps + (warp - 2);
-                reduce_mode = split_of(t) != 0;
-                if (reduce_mode) {
-                    // the other pair's plain stores of these boxes must be complete before this warp adds to them
-                    bool seen = true;
-                    if (issuer) {
-                        uint64_t t0 = 0;
-                        uint32_t spins = 0;
-                        while (ptx::ld_acquire_gpu_u32(split_flag) == 0u) {
-                            if ((++spins & 0x3Fu) == 0) {
-                                const uint64_t now = ptx::globaltimer_ns();
-                                if (t0 == 0) t0 = now;
-                                else if (now - t0 > kWaitLimitNs || *abort_flag) { seen = false; break; }
-                            }
-                        }
-                        if (seen) *split_flag = 0u;               // consumed: the next launch finds it zero
-                        ptx::fence_proxy_async_global();
-                    }
-                    seen = __all_sync(0xffffffffu, seen);
-                    if (!seen) {
-                        record_failure(args.status, abort_flag, kStatusEpilogueTimeout);
-                        skip_stores = true;                       // drain the accumulator, write nothing
-                    }
-                }
-            }
 
             // extended epilogue, in registers: t = alpha' * acc + beta * old D + bias (old D read row by row),
             // running |t| maximum over the valid part, then the output scale
@@ -670,9 +617,8 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (issuer) {
-                        if (row0 < args.M && col0 < args.N && !(kDiagnostics && (args.debug & 2)) && args.mc_c == nullptr && !skip_stores) {
-                            if (reduce_mode) ptx::tma_reduce_add_2d(&tmap_c, sb, col0, row0);
-                            else if (args.l2_stores) ptx::tma_store_2d_hint(&tmap_c, sb, col0, row0, store_policy);
+                        if (row0 < args.M && col0 < args.N && !(kDiagnostics && (args.debug & 2)) && args.mc_c == nullptr) {
+                            if (args.l2_stores) ptx::tma_store_2d_hint(&tmap_c, sb, col0, row0, store_policy);
                             else ptx::tma_store_2d(&tmap_c, sb, col0, row0);
                         }
                         ptx::bulk_commit_group();
@@ -760,17 +706,6 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (args.store_gap_ns) __nanosleep(args.store_gap_ns);
                 emit(vb, c + 1);
                 if (args.store_gap_ns && c + 2 < chunks) __nanosleep(args.store_gap_ns);
-            }
-            if (split_flag != nullptr && !reduce_mode) {
-                // first half of K: this warp's boxes are in C (complete, not merely read out of the staging box):
-                // let the warp that adds the second half go ahead
-                if (issuer) {
-                    ptx::bulk_wait_group<0>();
-                    ptx::fence_proxy_async_global();
-                    __threadfence();
-                    ptx::st_release_gpu_u32(split_flag, 1u);
-                }
-                __syncwarp();
             }
         }
         // the staging box must outlive the stores' reads of it; the writes themselves complete with the grid

@@ -189,12 +189,6 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
                  ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
                  : "memory");
 }
-// 2-D tiled reduction shared -> global: every element of the box is ADDED (FP32) to the element in memory, in L2
-__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, uint32_t src, int32_t x, int32_t y) {
-    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
-                 : "memory");
-}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {
@@ -203,16 +197,6 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-// orders this thread's generic-proxy accesses (flags) against its async-proxy accesses (TMA stores / reductions)
-__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
-__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_gpu_u32(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // make generic-proxy writes to shared memory visible to the async proxy (TMA store source)
 __device__ __forceinline__ void fence_proxy_async_smem() {

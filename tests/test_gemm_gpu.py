@@ -220,44 +220,6 @@ def test_stream_k_pieces_sum_in_fixed_order(g, oracle, m, k, n, max_pieces):
         assert torch.equal(x, y)
 
 
-@pytest.mark.parametrize("kernel,shape", [(3, (256, 4096 + 128, 520)), (3, (300, 8192, 1032)), (3, (512, 384, 512)), (1, (130, 1024, 516)),
-                                          (2, (256, 2048 + 16, 384)), (5, (256, 4096, 1024)), (6, (256, 1024, 640)), (7, (128, 512, 320)),
-                                          (0, (256, 8192, 8192)), (0, (200, 4096, 4096)), (0, (512, 8192, 4096))])
-@pytest.mark.parametrize("fa,fb", [(0, 0), (1, 0)])
-def test_two_way_k_split_of_the_tile_kernels(g, oracle, kernel, shape, fa, fb):
-    """K split over two CTA pairs: the pair with the first half of K stores its partial tile, the pair with the second
-    half adds its own with TMA reductions after the first pair's per-warp flag.  Two terms: the sum does not depend on
-    arrival order, so repeated launches (flags must come back as zero) agree bit for bit; the result holds the path's
-    tolerance; guard rows and pitch padding around C stay untouched.  kernel 0: shapes the automatic rule splits."""
-    m, k, n = shape
-    a, b = random_operands(g, m, k, n, fa, fb, seed=41 + kernel)
-    guard, ldc = 2, n + 8
-    buf = torch.full((m + 2 * guard, ldc), float("nan"), dtype=torch.float32, device="cuda")
-    c = buf[guard:guard + m]
-    kw = dict(kernel=kernel, ldc=ldc) if kernel == 0 else dict(kernel=kernel, split_k=2, ldc=ldc)
-    g.gemm_ex(a, b, c[:, :n], **kw)
-    torch.cuda.synchronize()
-    assert g.device_status() == 0
-    first = c[:, :n].clone()
-    for _ in range(3):
-        c[:, :n].fill_(float("nan"))
-        g.gemm_ex(a, b, c[:, :n], **kw)
-        torch.cuda.synchronize()
-        assert torch.equal(c[:, :n], first)
-    h = buf.cpu().numpy()
-    assert np.isnan(h[:guard]).all() and np.isnan(h[guard + m:]).all() and np.isnan(h[guard:guard + m, n:]).all()
-    if m * n * k <= 2 ** 32:
-        assert_within_tolerance(oracle, np.ascontiguousarray(h[guard:guard + m, :n]), host_bytes(a), fa, host_bytes(b), fb)
-    else:
-        sampled_check(oracle, a, b, first, fa, fb, rows=16, cols=16, points=4096)
-    # the unsplit result differs at most by the rounding of one more addition per element
-    whole = run(g, a, b, m, k, n, kernel=kernel or 3, split_k=1)
-    assert torch.allclose(first, whole, rtol=0, atol=4e-3 if fa == 0 else 4e-2)
-    if kernel == 0:
-        forced = run(g, a, b, m, k, n, kernel=3, split_k=2)
-        assert torch.equal(first, forced)          # the automatic rule took exactly this path
-
-
 def test_zero_k_and_empty(g):
     out = torch.full((8, 12), 3.0, dtype=torch.float32, device="cuda")
     a = torch.empty((8, 0), dtype=F8[0], device="cuda")
@@ -507,11 +469,7 @@ def test_row_permutation_and_row_blocks_are_bitwise(g):
     ap = a.view(torch.uint8)[perm].contiguous().view(a.dtype)
     assert torch.equal(run(g, ap, b, m, k, n), c[perm])
     for r0, r1 in ((0, 300), (1000, 1257), (4096 - 640, 4096)):          # 300 and 257 rows pick other kernels than 4096
-        # split_k=1: without the two-way split of K, which problems of so few tiles would otherwise get (it adds the
-        # two halves' sums, another order of summation: equal within rounding, not bit for bit)
-        assert torch.equal(run(g, a[r0:r1], b, r1 - r0, k, n, split_k=1), c[r0:r1])
-        auto = run(g, a[r0:r1], b, r1 - r0, k, n)
-        assert torch.allclose(auto, c[r0:r1], rtol=0, atol=2e-3)
+        assert torch.equal(run(g, a[r0:r1], b, r1 - r0, k, n), c[r0:r1])
 
 
 # ---------------------------------------------------------------- host-pointer entry point, generator, drop-in binary
