@@ -1,6 +1,7 @@
 """The reference benchmark driver's command line on top of this library, with working CSV output.
 
     python tensor-core-fp8_b200/sweep.py dimM dimK dimN kernel verify record testbench [--cublaslt] [--data-dir DIR]
+                                         [--jsonl FILE [--resume]] [--plot FILE.svg]
 
 Same seven positional arguments, kernel numbering, timing protocol and CSV lines as the
 reference driver (GEMM/gemm_main.cpp:196-313 argument handling, :25-26 and :69-84 timing:
@@ -17,12 +18,16 @@ Differences, on purpose: the data directory is created (the reference appends in
 that does not exist and silently records nothing); `verify` checks on the device in FP64
 (a random-vector product check of the whole C plus full rows against an FP64 matmul) instead
 of the O(MNK) single-thread CPU loop, so that it stays usable at 16384^3; `--cublaslt` records
-the comparator beside every shape in fp8_gemm_cublaslt.csv.
+the comparator beside every shape in fp8_gemm_cublaslt.csv; `--jsonl` appends one JSON object per measured
+(shape, kernel) and `--resume` skips what that file already holds, so an interrupted sweep continues where it
+stopped; `--plot` draws every CSV of the data directory (this library's kernels and cuBLASLt) as TFLOP/s over the
+cube size into one SVG file (no plotting package needed).
 """
 from __future__ import annotations
 
 import argparse
 import ctypes
+import json
 import os
 import sys
 
@@ -38,6 +43,9 @@ def parse(argv):
     ap.add_argument("--cublaslt", action="store_true", help="also time cuBLASLt on the same buffers and record it")
     ap.add_argument("--data-dir", default="./data")
     ap.add_argument("--max-dim", type=int, default=16384, help="largest cube of the sweep (the reference's is 16384)")
+    ap.add_argument("--jsonl", default=None, help="append one JSON object per measured (shape, kernel) to this file")
+    ap.add_argument("--resume", action="store_true", help="skip the (shape, kernel) pairs the --jsonl file already holds")
+    ap.add_argument("--plot", default=None, help="after the run, draw the CSV files of the data directory into this SVG file")
     args = ap.parse_args(argv)
     if args.kernel not in PAIRS:
         ap.error("kernel must be 1..9")
@@ -66,6 +74,92 @@ def record_line(data_dir, kernel, m, k, n, perf):
     with open(path, "a") as f:
         f.write(f"{m},{k},{n},{perf}\n")
     return path
+
+
+def jsonl_done(path):
+    """The (m, k, n, kernel) tuples a JSONL log already holds (lines that do not parse are ignored: a run that was
+    killed in the middle of a line must not block the resume)."""
+    done = set()
+    if path and os.path.exists(path):
+        with open(path) as f:
+            for line in f:
+                try:
+                    r = json.loads(line)
+                    done.add((int(r["m"]), int(r["k"]), int(r["n"]), int(r["kernel"])))
+                except (ValueError, KeyError, TypeError):
+                    continue
+    return done
+
+
+def jsonl_append(path, record):
+    d = os.path.dirname(os.path.abspath(path))
+    os.makedirs(d, exist_ok=True)
+    with open(path, "a") as f:
+        f.write(json.dumps(record) + "\n")
+        f.flush()
+        os.fsync(f.fileno())
+
+
+def read_csvs(data_dir):
+    """{label: [(m, gflops), ...]} of every CSV the sweep writes into `data_dir` (cube shapes only, sorted by size)."""
+    series = {}
+    if not os.path.isdir(data_dir):
+        return series
+    for name in sorted(os.listdir(data_dir)):
+        if not (name.startswith("fp8_gemm_") and name.endswith(".csv")):
+            continue
+        label = name[len("fp8_gemm_"):-len(".csv")]
+        pts = {}
+        with open(os.path.join(data_dir, name)) as f:
+            for line in f:
+                try:
+                    m, k, n, perf = line.strip().split(",")
+                    if int(m) == int(k) == int(n):
+                        pts[int(m)] = float(perf)          # a later line for the same shape replaces the earlier one
+                except ValueError:
+                    continue
+        if pts:
+            series[label] = sorted(pts.items())
+    return series
+
+
+def plot_svg(data_dir, out_path, width=960, height=540):
+    """TFLOP/s over the cube size, one polyline per CSV file, as a self-contained SVG (the reference plots nothing;
+    its CSV lines are what a plotting script would read: GEMM/gemm_main.cpp:87-110, GEMM/src/cublas.cu:126-134)."""
+    series = read_csvs(data_dir)
+    if not series:
+        return None
+    xs = [m for pts in series.values() for m, _ in pts]
+    ys = [p / 1000.0 for pts in series.values() for _, p in pts]
+    x0, x1, y1 = min(xs), max(xs), max(ys) * 1.05
+    left, right, top, bottom = 70, 190, 30, 50
+    pw, ph = width - left - right, height - top - bottom
+    sx = lambda m: left + (pw * (m - x0) / (x1 - x0) if x1 > x0 else pw / 2)
+    sy = lambda t: top + ph * (1 - t / y1)
+    colours = ["#1f77b4", "#d62728", "#2ca02c", "#9467bd", "#ff7f0e", "#8c564b", "#e377c2", "#17becf", "#7f7f7f"]
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="sans-serif" font-size="12">',
+           f'<rect width="{width}" height="{height}" fill="white"/>',
+           f'<text x="{left}" y="18" font-size="14">FP8 GEMM, M = K = N: TFLOP/s (reference protocol: mean of 100 synchronised calls)</text>']
+    for i in range(6):
+        t = y1 * i / 5
+        out.append(f'<line x1="{left}" y1="{sy(t):.1f}" x2="{left + pw}" y2="{sy(t):.1f}" stroke="#dddddd"/>')
+        out.append(f'<text x="{left - 8}" y="{sy(t) + 4:.1f}" text-anchor="end">{t:.0f}</text>')
+    for m in sorted(set(xs))[::max(1, len(set(xs)) // 8)]:
+        out.append(f'<text x="{sx(m):.1f}" y="{top + ph + 18}" text-anchor="middle">{m}</text>')
+    out.append(f'<rect x="{left}" y="{top}" width="{pw}" height="{ph}" fill="none" stroke="black"/>')
+    for i, (label, pts) in enumerate(series.items()):
+        c = colours[i % len(colours)]
+        path = " ".join(f"{sx(m):.1f},{sy(p / 1000.0):.1f}" for m, p in pts)
+        out.append(f'<polyline points="{path}" fill="none" stroke="{c}" stroke-width="2"/>')
+        for m, p in pts:
+            out.append(f'<circle cx="{sx(m):.1f}" cy="{sy(p / 1000.0):.1f}" r="2.5" fill="{c}"/>')
+        out.append(f'<rect x="{left + pw + 14}" y="{top + 18 * i}" width="12" height="12" fill="{c}"/>')
+        out.append(f'<text x="{left + pw + 32}" y="{top + 18 * i + 11}">{label}</text>')
+    out.append("</svg>")
+    os.makedirs(os.path.dirname(os.path.abspath(out_path)), exist_ok=True)
+    with open(out_path, "w") as f:
+        f.write("\n".join(out) + "\n")
+    return out_path
 
 
 def time_calls(call, torch):
@@ -144,6 +238,9 @@ def run_shape(pkg, torch, args, m, k, n):
         print(f"{label} Avager Performance = {perf:f} GFlops")
         if args.record:
             record_line(args.data_dir, kern, m, k, n, perf)
+        if args.jsonl:
+            jsonl_append(args.jsonl, {"m": m, "k": k, "n": n, "kernel": kern, "a": NAMES[fa], "b": NAMES[fb], "gflops": perf,
+                                      "protocol": f"{WARMUP} warm-up + {REPEAT} synchronised calls"})
     if args.verify and args.kernel != 9:
         worst = verify_on_device(torch, a, b, c)
         status = g.device_status()
@@ -171,8 +268,15 @@ def main(argv=None, pkg=None):
     fa, fb = PAIRS[args.kernel]
     print(f"{NAMES[fa]} * {NAMES[fb]} = fp32" if args.kernel != 9 else "cuBLASLt: e4m3 * e4m3 = fp32")
     rc = 0
+    done = jsonl_done(args.jsonl) if args.resume else set()
     for (m, k, n) in shapes(args):
+        if (m, k, n, args.kernel) in done:
+            print(f"M = {m}, K = {k}, N = {n}: already in {args.jsonl}, skipped")
+            continue
         rc |= run_shape(pkg, torch, args, m, k, n)
+    if args.plot:
+        out = plot_svg(args.data_dir, args.plot)
+        print(f"plot: {out if out else 'nothing recorded in ' + args.data_dir}")
     return rc
 
 

@@ -47,3 +47,29 @@ def test_record_creates_the_directory_and_appends(sweep, tmp_path):
     assert os.path.basename(p) == "fp8_gemm_v2.csv"
     assert open(p).read().splitlines() == ["256,256,256,1234.5", "512,512,512,99.0"]
     assert os.path.basename(sweep.record_line(d, 9, 1, 1, 1, 1.0)) == "fp8_gemm_cublaslt.csv"
+
+
+def test_jsonl_log_resumes_and_ignores_a_torn_last_line(sweep, tmp_path):
+    log = str(tmp_path / "runs" / "sweep.jsonl")
+    sweep.jsonl_append(log, {"m": 256, "k": 256, "n": 256, "kernel": 2, "gflops": 1.0})
+    sweep.jsonl_append(log, {"m": 512, "k": 512, "n": 512, "kernel": 2, "gflops": 2.0})
+    with open(log, "a") as f:
+        f.write('{"m": 768, "k": 768, "n"')                  # a run killed in the middle of a line
+    assert sweep.jsonl_done(log) == {(256, 256, 256, 2), (512, 512, 512, 2)}
+    assert sweep.jsonl_done(str(tmp_path / "absent.jsonl")) == set()
+    a = sweep.parse("1 1 1 2 0 1 1 --jsonl x.jsonl --resume --plot y.svg".split())
+    assert a.jsonl == "x.jsonl" and a.resume and a.plot == "y.svg"
+
+
+def test_plot_draws_one_line_per_csv(sweep, tmp_path):
+    d = str(tmp_path / "data")
+    assert sweep.plot_svg(d, str(tmp_path / "none.svg")) is None        # nothing recorded yet
+    for size, ours, lt in ((256, 900.0, 1000.0), (512, 8000.0, 9000.0), (1024, 400000.0, 450000.0)):
+        sweep.record_line(d, 2, size, size, size, ours)
+        sweep.record_line(d, 9, size, size, size, lt)
+    sweep.record_line(d, 2, 128, 64, 32, 5.0)                           # not a cube: left out of the plot
+    series = sweep.read_csvs(d)
+    assert set(series) == {"v2", "cublaslt"} and [m for m, _ in series["v2"]] == [256, 512, 1024]
+    out = sweep.plot_svg(d, str(tmp_path / "plots" / "sweep.svg"))
+    svg = open(out).read()
+    assert svg.startswith("<svg") and svg.count("<polyline") == 2 and "cublaslt" in svg and "v2" in svg
