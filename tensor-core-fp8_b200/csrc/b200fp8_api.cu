@@ -191,14 +191,14 @@ struct EllSpec {
     int blocks;
 };
 
-template <int BN, int STAGES, int CTAS, int NACC>
+template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1>
 cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
                         const PeerSet* peers, const Epilogue* epi, cudaStream_t stream, const EllSpec* ell = nullptr) {
-    using L = GemmSmem<BN, STAGES, CTAS, NACC>;
+    using L = GemmSmem<BN, STAGES, CTAS, NACC, KPS>;
     static bool attr_done[kMaxDevices] = {};
     if (ell && CTAS != 1) return cudaErrorInvalidValue;       // a block row is one 128-row M-tile
-    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC>;
+    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC, KPS>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev]) {
@@ -373,22 +373,23 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     if (peers && (peers->count > 0 || peers->multicast) && (kernel == B200FP8_KERNEL_SKINNY || kernel == B200FP8_KERNEL_SKINNY_STREAMK))
         kernel = B200FP8_KERNEL_PAIR_N256;
 
-#define B200FP8_LAUNCH(BN, ST, CT) B200FP8_LAUNCH4(BN, ST, CT, 1)
-#define B200FP8_LAUNCH4(BN, ST, CT, NA) \
-    launch_main<BN, ST, CT, NA>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell)
+    // Ring depth: `depth` stages in flight (2 = gemm::GEMM, 4 = gemm::GEMM4), each stage as many 128-byte k-blocks as
+    // shared memory holds (KPS); depth 0 = one k-block per stage, as many stages as fit.
+#define B200FP8_LAUNCH5(BN, ST, CT, NA, KPS) \
+    launch_main<BN, ST, CT, NA, KPS>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
-            return depth == 2 ? B200FP8_LAUNCH(256, 2, 1) : B200FP8_LAUNCH(256, 4, 1);
+            return depth == 2 ? B200FP8_LAUNCH5(256, 2, 1, 1, 2) : B200FP8_LAUNCH5(256, 4, 1, 1, 1);
         case B200FP8_KERNEL_CTA1_N128:
-            return depth == 2 ? B200FP8_LAUNCH(128, 2, 1) : depth == 4 ? B200FP8_LAUNCH(128, 4, 1) : B200FP8_LAUNCH(128, 6, 1);
+            return depth == 2 ? B200FP8_LAUNCH5(128, 2, 1, 1, 3) : depth == 4 ? B200FP8_LAUNCH5(128, 4, 1, 1, 1) : B200FP8_LAUNCH5(128, 6, 1, 1, 1);
         case B200FP8_KERNEL_PAIR_N256:
-            return depth == 2 ? B200FP8_LAUNCH(256, 2, 2) : depth == 4 ? B200FP8_LAUNCH(256, 4, 2) : B200FP8_LAUNCH(256, 6, 2);
+            return depth == 2 ? B200FP8_LAUNCH5(256, 2, 2, 1, 3) : depth == 4 ? B200FP8_LAUNCH5(256, 4, 2, 1, 1) : B200FP8_LAUNCH5(256, 6, 2, 1, 1);
         case B200FP8_KERNEL_CTA1_N64:
-            return depth == 2 ? B200FP8_LAUNCH(64, 2, 1) : depth == 4 ? B200FP8_LAUNCH(64, 4, 1) : B200FP8_LAUNCH(64, 8, 1);
+            return depth == 2 ? B200FP8_LAUNCH5(64, 2, 1, 1, 4) : depth == 4 ? B200FP8_LAUNCH5(64, 4, 1, 1, 2) : B200FP8_LAUNCH5(64, 8, 1, 1, 1);
         case B200FP8_KERNEL_PAIR_N128:
-            return depth == 2 ? B200FP8_LAUNCH(128, 2, 2) : depth == 4 ? B200FP8_LAUNCH(128, 4, 2) : B200FP8_LAUNCH(128, 8, 2);
+            return depth == 2 ? B200FP8_LAUNCH5(128, 2, 2, 1, 4) : depth == 4 ? B200FP8_LAUNCH5(128, 4, 2, 1, 2) : B200FP8_LAUNCH5(128, 8, 2, 1, 1);
         case B200FP8_KERNEL_PAIR_N512:
-            return depth == 2 ? B200FP8_LAUNCH4(256, 2, 2, 2) : B200FP8_LAUNCH4(256, 4, 2, 2);
+            return depth == 2 ? B200FP8_LAUNCH5(256, 2, 2, 2, 2) : B200FP8_LAUNCH5(256, 4, 2, 2, 1);
         case B200FP8_KERNEL_SKINNY: {
             if (split_k > kSkinnyMaxSplits) return cudaErrorInvalidValue;
             long long* trace = nullptr;
@@ -417,8 +418,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         default:
             return cudaErrorInvalidValue;
     }
-#undef B200FP8_LAUNCH
-#undef B200FP8_LAUNCH4
+#undef B200FP8_LAUNCH5
 }
 
 cudaError_t ensure(void** p, size_t* have, size_t want) {

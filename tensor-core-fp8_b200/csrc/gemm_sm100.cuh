@@ -212,17 +212,20 @@ __device__ __forceinline__ void record_failure(int* status, volatile int* abort_
     __threadfence_block();
 }
 
-template <int BN, int STAGES, int CTAS, int NACC>
+// STAGES ring stages of KPS k-blocks each: a stage is loaded, awaited, consumed and released as a whole (one full and
+// one empty barrier per stage), so "2-stage" (gemm::GEMM) means two stages in flight, each as many k-blocks as fit.
+template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1>
 struct GemmSmem {
+    static constexpr int kSlots = STAGES * KPS;              // k-block slots in the ring
     static constexpr int kABytes = kTileM * kBlockK;
     static constexpr int kBRows = BN / CTAS;                 // rows of one B sub-tile held by this CTA
     static constexpr int kBBytes = kBRows * kBlockK;
-    static constexpr int kStageBytes = kABytes + NACC * kBBytes;
-    static constexpr int kTxBytes = kStageBytes * CTAS;      // bytes landing per ring slot across the pair
+    static constexpr int kStageBytes = kABytes + NACC * kBBytes;   // bytes of one k-block slot
+    static constexpr int kTxBytes = kStageBytes * CTAS;      // bytes landing per k-block slot across the pair
     static constexpr int kEpiBufBytes = 32 * 32 * 4;         // one 32x32 FP32 box
     static constexpr int kEpiBytes = kEpiWarps * kEpiBufBytes;   // one staging box per epilogue warp
     static constexpr int kRingOff = 0;
-    static constexpr int kEpiOff = STAGES * kStageBytes;
+    static constexpr int kEpiOff = kSlots * kStageBytes;
     static constexpr int kBarOff = kEpiOff + kEpiBytes;      // full[STAGES] empty[STAGES] tfull[2] tempty[2]
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemSlotOff = kBarOff + 8 * kNumBars;
@@ -233,7 +236,7 @@ struct GemmSmem {
     static constexpr int kTileN = BN * NACC;                 // columns of C per tile
 };
 
-template <int BN, int STAGES, int CTAS, int NACC>
+template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
@@ -241,7 +244,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b_half,   // B with boxes of half as many rows (tail items)
                        const GemmArgs args)
 {
-    using L = GemmSmem<BN, STAGES, CTAS, NACC>;
+    using L = GemmSmem<BN, STAGES, CTAS, NACC, KPS>;
     static_assert(BN % 32 == 0 && BN <= 256 && (BN / CTAS) % 8 == 0 && (NACC == 1 || NACC == 2), "tile");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -295,6 +298,9 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int first_tile = blockIdx.x / CTAS;
     const int tile_step = gridDim.x / CTAS;
     const int nkb = args.num_k_blocks;
+    // k-blocks this CTA streams over all of its work items: the last stage of the stream may hold fewer than KPS
+    const long long stream_kb = first_tile < num_items
+        ? static_cast<long long>((num_items - first_tile + tile_step - 1) / tile_step) * nkb : 0;
 
     // work item -> first row / column of this CTA's part; `half` = half-width tail item
     auto tile_coords = [&](int t, int& m0, int& n0, bool& half) {
@@ -324,9 +330,10 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // ---------------- TMA producer: warp-uniform loop, one elected lane issues ----------------
         const uint32_t full0 = pair ? ptx::mapa(bar_full, 0) : bar_full;   // the leader's full barriers
         const uint64_t load_policy = ptx::l2_policy(args.l2_loads);
-        int s = 0;
+        int s = 0;                       // k-block slot; its stage is s / KPS
         uint32_t ph = 0;
         int issued = 0;
+        long long streamed = 0;
         bool ok = true;
         int it = 0;
         for (int t = first_tile; t < num_items && ok; t += tile_step, ++it) {
@@ -358,7 +365,10 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (lane < nkb) ell_nxt = ell_row[lane];
             }
             for (int kb = 0; kb < nkb; ++kb) {
-                if (!wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
+                const int stage = s / KPS;
+                const bool stage_first = (s % KPS) == 0;
+                const bool stage_last = (s % KPS) == KPS - 1 || streamed + 1 == stream_kb;
+                if (stage_first && !wait_bounded(bar_empty + 8 * stage, ph ^ 1u, abort_flag, pair, args.wait_hint_ns)) {
                     record_failure(args.status, abort_flag, kStatusProducerTimeout);
                     ok = false;
                     break;
@@ -375,43 +385,52 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 const uint32_t a_dst = smem_base + L::kRingOff + s * L::kStageBytes;
                 const uint32_t b_dst = a_dst + L::kABytes;
-                if ((args.debug & 512) && it == 0 && kb == 2) {
+                if (KPS == 1 && (args.debug & 512) && it == 0 && kb == 2) {
                     // failure-path test: this ring slot is never armed nor loaded, so the MMA warp's bounded wait on
                     // it must run out and the kernel must end by itself with a status code
                 } else if (ptx::elect_one()) {
+                    const uint32_t fullb = bar_full + 8 * stage;           // this CTA's barrier of the stage
+                    const uint32_t fullr = full0 + 8 * stage;              // the leader's, where the copies signal
                     if (kDiagnostics && (args.debug & 1)) {
-                        if (rank == 0) ptx::mbar_arrive(bar_full + 8 * s);
-                    } else if (pair) {
-                        if (rank == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
-                        if (args.l2_loads) {
-                            ptx::tma_load_2d_pair_hint(a_dst, &tmap_a, ka, m0, full0 + 8 * s, load_policy);
-#pragma unroll
-                            for (int j = 0; j < NACC; ++j)
-                                ptx::tma_load_2d_pair_hint(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, full0 + 8 * s, load_policy);
-                        } else {
-                            ptx::tma_load_2d_pair(a_dst, &tmap_a, ka, m0, full0 + 8 * s);
-#pragma unroll
-                            for (int j = 0; j < NACC; ++j)
-                                ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, full0 + 8 * s);
-                        }
+                        if (rank == 0 && stage_last) ptx::mbar_arrive(fullb);
                     } else {
-                        ptx::mbar_arrive_expect_tx(bar_full + 8 * s, tx_bytes);
-                        if (args.l2_loads) {
-                            ptx::tma_load_2d_hint(a_dst, &tmap_a, ka, m0, bar_full + 8 * s, load_policy);
+                        // the stage's byte count grows k-block by k-block; the single arrival that can close the phase
+                        // comes with the stage's last k-block
+                        if (rank == 0) {
+                            if (stage_last) ptx::mbar_arrive_expect_tx(fullb, tx_bytes);
+                            else ptx::mbar_expect_tx(fullb, tx_bytes);
+                        }
+                        if (pair) {
+                            if (args.l2_loads) {
+                                ptx::tma_load_2d_pair_hint(a_dst, &tmap_a, ka, m0, fullr, load_policy);
 #pragma unroll
-                            for (int j = 0; j < NACC; ++j)
-                                ptx::tma_load_2d_hint(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, bar_full + 8 * s, load_policy);
+                                for (int j = 0; j < NACC; ++j)
+                                    ptx::tma_load_2d_pair_hint(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, fullr, load_policy);
+                            } else {
+                                ptx::tma_load_2d_pair(a_dst, &tmap_a, ka, m0, fullr);
+#pragma unroll
+                                for (int j = 0; j < NACC; ++j)
+                                    ptx::tma_load_2d_pair(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, fullr);
+                            }
                         } else {
-                            ptx::tma_load_2d(a_dst, &tmap_a, ka, m0, bar_full + 8 * s);
+                            if (args.l2_loads) {
+                                ptx::tma_load_2d_hint(a_dst, &tmap_a, ka, m0, fullb, load_policy);
 #pragma unroll
-                            for (int j = 0; j < NACC; ++j)
-                                ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, bar_full + 8 * s);
+                                for (int j = 0; j < NACC; ++j)
+                                    ptx::tma_load_2d_hint(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, fullb, load_policy);
+                            } else {
+                                ptx::tma_load_2d(a_dst, &tmap_a, ka, m0, fullb);
+#pragma unroll
+                                for (int j = 0; j < NACC; ++j)
+                                    ptx::tma_load_2d(b_dst + j * L::kBBytes, tmb, kbx, nb0 + j * BN, fullb);
+                            }
                         }
                     }
                 }
                 __syncwarp();
                 ++issued;
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
+                ++streamed;
+                if (++s == L::kSlots) { s = 0; ph ^= 1u; }
             }
         }
         if (args.pace != nullptr && rank == 0) {
@@ -421,13 +440,16 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             __syncwarp();
         }
         if (!ok && rank == 0) {
-            // leave no copy in flight into this CTA's shared memory: wait (bounded) for the slots armed last
-            const int pending = issued < STAGES ? issued : STAGES;
+            // leave no copy in flight into this CTA's shared memory: close a stage that was left half armed, then wait
+            // (bounded) for the stages armed last
+            if ((s % KPS) != 0 && ptx::elect_one()) ptx::mbar_arrive(bar_full + 8 * (s / KPS));
+            __syncwarp();
+            const int pending = issued < L::kSlots ? issued : L::kSlots;
             for (int i = 0; i < pending; ++i) {
-                if (s == 0) { s = STAGES; ph ^= 1u; }
+                if (s == 0) { s = L::kSlots; ph ^= 1u; }
                 --s;
                 const uint64_t t0 = ptx::globaltimer_ns();
-                while (!ptx::mbar_try_wait(bar_full + 8 * s, ph) && ptx::globaltimer_ns() - t0 < kWaitLimitNs) {}
+                while (!ptx::mbar_try_wait(bar_full + 8 * (s / KPS), ph) && ptx::globaltimer_ns() - t0 < kWaitLimitNs) {}
             }
         }
     } else if (warp == 1) {
@@ -436,6 +458,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
+            long long streamed = 0;
             bool ok = true;
             for (int t = first_tile; t < num_items && ok; t += tile_step, ++it) {
                 const uint32_t idesc = (t >= args.full_items) ? args.idesc_half : args.idesc;
@@ -449,7 +472,9 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 for (int kb = 0; kb < nkb; ++kb) {
                     long long tr0 = 0, tr1 = 0;
                     if (kDiagnostics && (args.debug & 64) && blockIdx.x == 0) tr0 = clock64();
-                    if (!wait_bounded(bar_full + 8 * s, ph, abort_flag, pair, args.wait_hint_ns)) {
+                    const int stage = s / KPS;
+                    const bool stage_last = (s % KPS) == KPS - 1 || streamed + 1 == stream_kb;
+                    if ((s % KPS) == 0 && !wait_bounded(bar_full + 8 * stage, ph, abort_flag, pair, args.wait_hint_ns)) {
                         record_failure(args.status, abort_flag, kStatusMmaTimeout);
                         ok = false;
                         break;
@@ -478,16 +503,17 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         __syncwarp();
                     }
                     if (!ok) break;
-                    if (ptx::elect_one()) {
-                        if (pair) ptx::umma_commit_pair(bar_empty + 8 * s, 0x3);
-                        else ptx::umma_commit(bar_empty + 8 * s);
+                    if (stage_last && ptx::elect_one()) {                 // the whole stage has been read: hand it back
+                        if (pair) ptx::umma_commit_pair(bar_empty + 8 * stage, 0x3);
+                        else ptx::umma_commit(bar_empty + 8 * stage);
                     }
                     __syncwarp();
+                    ++streamed;
                     if (kDiagnostics && (args.debug & 64) && blockIdx.x == 0 && lane == 0) {
                         const int idx = it * nkb + kb;
                         if (idx < 4096) { args.trace[3 * idx] = tr0; args.trace[3 * idx + 1] = tr1; args.trace[3 * idx + 2] = clock64(); }
                     }
-                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    if (++s == L::kSlots) { s = 0; ph ^= 1u; }
                 }
                 if (ok && ptx::elect_one()) {
 #pragma unroll
