@@ -70,7 +70,7 @@ NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
 NVLINK_PEER_COPY_GBS = 770.0      # measured peer-copy rate per direction per GPU on this pool (nominal 900)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from one ncu capture at N = 1
-NCU_TRAFFIC_BYTES = {"shard32768": 30.11e9, "gemm8192": 537.6e6, "skinny16": 67.8e6}
+NCU_TRAFFIC_BYTES = {"shard32768": 30.11e9, "gemm8192": 547.7e6, "skinny16": 67.84e6, "skinny128": 69.3e6}
 DTYPE_NAMES = {0: "e4m3", 1: "e5m2"}
 
 
@@ -379,7 +379,7 @@ def measure_config(torch, g, cmp, dev, name, M, K, N, fa, fb, depth, kernel, pea
     iters = int(max(4, min(48, 2.5e-3 / est)))
     long_step = flops >= 2e12
     if long_step:
-        iters = 6
+        iters = 10
     stream = torch.cuda.current_stream().cuda_stream
     have_cmp = cmp.choose(M, K, N, a, fa, bs[0], fb, cs[0], stream)
 

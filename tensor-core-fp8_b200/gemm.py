@@ -48,11 +48,10 @@ def _check_extent(name: str, t: torch.Tensor, rows: int, cols: int, ld: int) -> 
     if ld < cols:
         raise ValueError(f"{name}: leading dimension {ld} is smaller than its {cols} columns")
     need = (rows - 1) * ld + cols
-    # elements reachable from data_ptr(): the tensor's own span (views of larger buffers may carry a pitch)
+    # elements reachable from data_ptr() through the tensor's own shape and strides (a view of a wider buffer has a pitch)
     span = 1 + sum((sz - 1) * st for sz, st in zip(t.shape, t.stride())) if t.numel() else 0
-    avail = max(span, (t.shape[0] - 1) * t.stride(0) + (t.shape[1] if t.dim() == 2 else 1) if t.dim() == 2 and t.numel() else span)
-    if need > avail:
-        raise ValueError(f"{name}: needs {need} elements ({rows} rows of {cols}, pitch {ld}) but the tensor spans {avail}")
+    if need > span:
+        raise ValueError(f"{name}: needs {need} elements ({rows} rows of {cols}, pitch {ld}) but the tensor spans {span}")
 
 
 def _check_operands(m, k, n, a, b, out, lda, ldb, ldc, out_name="out"):
