@@ -191,14 +191,15 @@ struct EllSpec {
     int blocks;
 };
 
-template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1>
+template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1, int AROWS = kTileM>
 cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long long lda, const void* b,
                         long long ldb, float* c, long long ldc, int a_dtype, int b_dtype, int max_ctas,
                         const PeerSet* peers, const Epilogue* epi, cudaStream_t stream, const EllSpec* ell = nullptr) {
-    using L = GemmSmem<BN, STAGES, CTAS, NACC, KPS>;
+    using L = GemmSmem<BN, STAGES, CTAS, NACC, KPS, AROWS>;
     static bool attr_done[kMaxDevices] = {};
+    if (AROWS < kTileM && (m > AROWS || ell)) return cudaErrorInvalidValue;   // the short A box holds the whole M
     if (ell && CTAS != 1) return cudaErrorInvalidValue;       // a block row is one 128-row M-tile
-    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC, KPS>;
+    auto kernel = gemm_fp8_rowcol_kernel<BN, STAGES, CTAS, NACC, KPS, AROWS>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_done[dev]) {
@@ -248,7 +249,7 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     CUtensorMap ta, tb, tc;
     cudaError_t e;
     const long long a_cols = ell ? static_cast<long long>(ell->blocks) * kBlockK : k;
-    if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, a_cols, m, lda, kBlockK, kTileM)) != cudaSuccess) return e;
+    if ((e = encode_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, a_cols, m, lda, kBlockK, AROWS)) != cudaSuccess) return e;
     if ((e = encode_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, k, n, ldb, kBlockK, L::kBRows)) != cudaSuccess) return e;
     if (args.tma_store && out_bytes == 1) {
         if ((e = encode_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, c, n, m, ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE)) != cudaSuccess) return e;
@@ -377,6 +378,8 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     // shared memory holds (KPS); depth 0 = one k-block per stage, as many stages as fit.
 #define B200FP8_LAUNCH5(BN, ST, CT, NA, KPS) \
     launch_main<BN, ST, CT, NA, KPS>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell)
+#define B200FP8_LAUNCH6(BN, ST, CT, NA, KPS, AR) \
+    launch_main<BN, ST, CT, NA, KPS, AR>(*ctx, m, k, n, a, lda, b, ldb, c, ldc, a_dtype, b_dtype, max_ctas, peers, epi, stream, ell)
     switch (kernel) {
         case B200FP8_KERNEL_CTA1_N256:
             return depth == 2 ? B200FP8_LAUNCH5(256, 2, 1, 1, 2) : B200FP8_LAUNCH5(256, 4, 1, 1, 1);
@@ -385,6 +388,10 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         case B200FP8_KERNEL_PAIR_N256:
             return depth == 2 ? B200FP8_LAUNCH5(256, 2, 2, 1, 3) : depth == 4 ? B200FP8_LAUNCH5(256, 4, 2, 1, 1) : B200FP8_LAUNCH5(256, 6, 2, 1, 1);
         case B200FP8_KERNEL_CTA1_N64:
+            // at most 64 rows and no sparse A: the short A box (16 / 32 / 64 rows), 18 / 16 / 12 k-blocks of B in flight
+            if (depth == 0 && !ell && m <= 16) return B200FP8_LAUNCH6(64, 9, 1, 1, 2, 16);
+            if (depth == 0 && !ell && m <= 32) return B200FP8_LAUNCH6(64, 8, 1, 1, 2, 32);
+            if (depth == 0 && !ell && m <= 64) return B200FP8_LAUNCH6(64, 6, 1, 1, 2, 64);
             return depth == 2 ? B200FP8_LAUNCH5(64, 2, 1, 1, 4) : depth == 4 ? B200FP8_LAUNCH5(64, 4, 1, 1, 2) : B200FP8_LAUNCH5(64, 8, 1, 1, 1);
         case B200FP8_KERNEL_PAIR_N128:
             return depth == 2 ? B200FP8_LAUNCH5(128, 2, 2, 1, 4) : depth == 4 ? B200FP8_LAUNCH5(128, 4, 2, 1, 2) : B200FP8_LAUNCH5(128, 8, 2, 1, 1);
@@ -419,6 +426,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
             return cudaErrorInvalidValue;
     }
 #undef B200FP8_LAUNCH5
+#undef B200FP8_LAUNCH6
 }
 
 cudaError_t ensure(void** p, size_t* have, size_t want) {

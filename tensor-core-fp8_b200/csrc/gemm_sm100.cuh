@@ -214,10 +214,13 @@ __device__ __forceinline__ void record_failure(int* status, volatile int* abort_
 
 // STAGES ring stages of KPS k-blocks each: a stage is loaded, awaited, consumed and released as a whole (one full and
 // one empty barrier per stage), so "2-stage" (gemm::GEMM) means two stages in flight, each as many k-blocks as fit.
-template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1>
+// AROWS < 128 (one-CTA kernels, problems of at most AROWS rows): the A box holds only AROWS rows, so a slot shrinks to
+// AROWS + BN rows and the ring holds more k-blocks of B in flight (decode-shaped problems stream B from HBM).  The MMA
+// still reads 128 rows from the slot's start; what lies behind the box feeds accumulator rows that are never stored.
+template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1, int AROWS = kTileM>
 struct GemmSmem {
     static constexpr int kSlots = STAGES * KPS;              // k-block slots in the ring
-    static constexpr int kABytes = kTileM * kBlockK;
+    static constexpr int kABytes = AROWS * kBlockK;
     static constexpr int kBRows = BN / CTAS;                 // rows of one B sub-tile held by this CTA
     static constexpr int kBBytes = kBRows * kBlockK;
     static constexpr int kStageBytes = kABytes + NACC * kBBytes;   // bytes of one k-block slot
@@ -236,7 +239,7 @@ struct GemmSmem {
     static constexpr int kTileN = BN * NACC;                 // columns of C per tile
 };
 
-template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1>
+template <int BN, int STAGES, int CTAS, int NACC, int KPS = 1, int AROWS = kTileM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b,
@@ -244,7 +247,8 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                        const __grid_constant__ CUtensorMap tmap_b_half,   // B with boxes of half as many rows (tail items)
                        const GemmArgs args)
 {
-    using L = GemmSmem<BN, STAGES, CTAS, NACC, KPS>;
+    using L = GemmSmem<BN, STAGES, CTAS, NACC, KPS, AROWS>;
+    static_assert(AROWS == kTileM || (CTAS == 1 && NACC == 1 && AROWS % 8 == 0), "short A boxes: one-CTA kernels only");
     static_assert(BN % 32 == 0 && BN <= 256 && (BN / CTAS) % 8 == 0 && (NACC == 1 || NACC == 2), "tile");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;

@@ -140,6 +140,8 @@ def test_special_values_propagate(g, oracle):
     (8, 0, (64, 256, 20000)), (8, 0, (1, 128 * 150, 128)), (8, 0, (128, 4096, 2500)),
     (6, 2, (256, 400, 512)), (6, 4, (200, 208, 516)), (6, 0, (700, 1024, 900)),
     (7, 2, (256, 400, 512)), (7, 4, (200, 208, 516)), (7, 0, (700, 1024, 900)),
+    (7, 0, (16, 1024, 1000)), (7, 0, (7, 8192 + 16, 520)), (7, 0, (33, 528, 260)), (7, 0, (64, 4096, 2500)), (7, 0, (1, 2048, 8192)),
+    (7, 0, (32, 144, 20000)),
     (0, 0, (640, 256, 896)),
 ])
 def test_random_operands_all_kernels(g, oracle, fa, fb, kernel, depth, shape):
@@ -281,7 +283,8 @@ def test_scaled_epilogue_with_unit_factors_equals_plain_operator(g):
 @pytest.mark.parametrize("kernel,m,n,ldc", [(2, 130, 132, 160), (3, 300, 260, 264), (1, 129, 257, 257), (4, 20, 130, 131),
                                             (3, 300, 1030, 1032), (5, 512, 1029, 1032), (1, 130, 259, 260), (2, 130, 130, 132),
                                             (5, 300, 772, 776), (5, 257, 515, 515),
-                                            (4, 100, 260, 272), (8, 20, 130, 131), (8, 100, 260, 272), (8, 128, 1027, 1028)])
+                                            (4, 100, 260, 272), (8, 20, 130, 131), (8, 100, 260, 272), (8, 128, 1027, 1028),
+                                            (7, 20, 130, 131), (7, 60, 260, 272), (7, 9, 1028, 1032)])
 def test_no_write_outside_c(g, oracle, kernel, m, n, ldc):
     k = 192
     a, b = random_operands(g, m, k, n, 0, 0, seed=9)
