@@ -628,22 +628,48 @@ def run_sparse(args, g, torch, dev, json_fd):
 
 
 def run_phase_timeline(args, g, torch, dev, json_fd, pkg):
-    """Where one launch of the M <= 128 kernels spends its time, from the kernels' own %globaltimer stamps.  Needs the
-    diagnostics build of the library (make -C tensor-core-fp8_b200/csrc diag; B200FP8_LIBRARY points at it and
-    B200FP8_DEBUG=1024 switches the stamps on): the product build has no such code."""
+    """Where one launch spends its time, from the kernels' own %globaltimer stamps: the phases of the M <= 128 kernels
+    (B200FP8_DEBUG=1024), or the epilogue chain of the tile kernels (M > 128 workloads, B200FP8_DEBUG=4096).  Needs the
+    diagnostics build of the library (make -C tensor-core-fp8_b200/csrc diag; B200FP8_LIBRARY points at it): the product
+    build has no such code."""
     import numpy as np
     lib = pkg._cabi.lib()
     if not hasattr(lib, "b200fp8_debug_trace_copy"):
         raise SystemExit("--phase-timeline needs the diagnostics build: B200FP8_LIBRARY=.../libb200fp8_diag.so B200FP8_DEBUG=1024")
     lib.b200fp8_debug_trace_copy.argtypes = [ctypes.POINTER(ctypes.c_longlong), ctypes.c_int, ctypes.c_int]
     M, K, N, _ = WORKLOADS[args.workload]
+    if M > 128:
+        # tile kernels (B200FP8_DEBUG=4096): the epilogue chain of CTA 0's first epilogue warp on its last work item --
+        # accumulator complete, then per 32-column chunk: in registers / staging box free / staged / fenced / store issued,
+        # finally: last store has read its box / all stores complete -- nanoseconds after the first stamp
+        f8 = torch.float8_e4m3fn
+        a = torch.empty((M, K), dtype=f8, device=dev)
+        b = torch.empty((N, K), dtype=f8, device=dev)
+        g.fill_normal(a, 1.0, 1)
+        g.fill_normal(b, 1.0, 2)
+        c = torch.empty((M, N), dtype=torch.float32, device=dev)
+        for _ in range(3):
+            g.gemm_ex(a, b, c, kernel=args.kernel, depth=args.depth)
+        torch.cuda.synchronize()
+        buf = (ctypes.c_longlong * 64)()
+        lib.b200fp8_debug_trace_copy(buf, 64, 1)
+        g.gemm_ex(a, b, c, kernel=args.kernel, depth=args.depth)
+        torch.cuda.synchronize()
+        lib.b200fp8_debug_trace_copy(buf, 64, 1)
+        t = [int(x) for x in buf[:32] if x > 0]
+        line = {"epilogue_chain_ns": [x - t[0] for x in t] if t else [],
+                "config": {"workload": args.workload, "M": M, "K": K, "N": N, "kernel": args.kernel, "depth": args.depth},
+                "stamps": "accumulator complete; per chunk: [in registers (even chunks),] box free, staged, fenced, issued; "
+                          "last store has read its box; all stores complete"}
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+        return 0
     kernel = args.kernel or 4
     names = {4: ["entry", "set-up done", "first block in shared memory", "accumulator complete", "epilogue woke",
                  "first cluster barrier passed", "reduce-scatter + stores done", "end"],
              8: ["entry", "grid dependency wait passed", "first block in shared memory", "MMA warp done",
                  "finisher saw its peers' flags", "finisher's first bulk copy landed", "epilogue done", "end"]}.get(kernel)
-    if names is None or M > 128:
-        raise SystemExit("--phase-timeline covers the M <= 128 kernels (--kernel 4 or 8)")
+    if names is None:
+        raise SystemExit("--phase-timeline of an M <= 128 workload takes --kernel 4 or 8")
     f8 = torch.float8_e4m3fn
     a = torch.empty((M, K), dtype=f8, device=dev)
     g.fill_normal(a, 1.0, 1)

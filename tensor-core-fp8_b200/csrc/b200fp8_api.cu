@@ -224,8 +224,8 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
     args.debug = tune().debug;
     args.store_gap_ns = (NACC == 1) ? static_cast<unsigned int>(tune().store_gap_ns) : 0u;
 #ifdef B200FP8_DIAGNOSTICS
-    if (args.debug & (64 | 128)) args.trace = trace_buffer();
-    if (!args.trace) args.debug &= ~(64 | 128);
+    if (args.debug & (64 | 128 | 4096)) args.trace = trace_buffer();
+    if (!args.trace) args.debug &= ~(64 | 128 | 4096);
 #endif
     args.idesc = make_idesc_f8(a_dtype, b_dtype, kTileM * CTAS, BN);
     const int out_bytes = epi ? out_dtype_bytes(epi->out_dtype) : 4;

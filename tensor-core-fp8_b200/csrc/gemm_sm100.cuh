@@ -563,6 +563,11 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + slot * BN + c_first * 32;
             const int col_base = n0 + (NACC == 2 ? grp * BN : 0) + c_first * 32;
 
+            // diagnostics build: time stamps along the epilogue chain of one warp (CTA 0, last item)
+            long long* etrace = (kDiagnostics && (args.debug & 4096) && args.trace && blockIdx.x == 0 && warp == 2 && lane == 0 &&
+                                 t + tile_step >= num_items) ? args.trace : nullptr;
+            int estamp = 0;
+            auto stamp = [&]() { if (etrace && estamp < 30) etrace[estamp++] = static_cast<long long>(ptx::globaltimer_ns()); };
             // extended epilogue, in registers: t = alpha' * acc + beta * old D + bias (old D read row by row),
             // running |t| maximum over the valid part, then the output scale
             auto scale = [&](uint32_t (&v)[32], int c) {
@@ -640,12 +645,15 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 } else if (args.tma_store) {
                     if (issuer) ptx::bulk_wait_group_read<0>();   // the previous store has finished reading the box
                     __syncwarp();
+                    stamp();                                      // box free
                     const uint32_t row_addr = sb + lane * 128;
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         ptx::st_shared_v4(row_addr + ((i ^ (lane & 7)) << 4), v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    stamp();                                      // staged
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
+                    stamp();                                      // fenced
                     if (issuer) {
                         if (row0 < args.M && col0 < args.N && !(kDiagnostics && (args.debug & 2)) && args.mc_c == nullptr) {
                             if (args.l2_stores) ptx::tma_store_2d_hint(&tmap_c, sb, col0, row0, store_policy);
@@ -714,6 +722,7 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
             };
 
+            stamp();                                              // accumulator complete
             // two register sets: the TMEM load of chunk c+1 is in flight while chunk c is stored
             uint32_t va[32], vb[32];
             ptx::tmem_ld_32x32(t_addr, va);
@@ -726,16 +735,25 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 1
             for (int c = 0; c < chunks; c += 2) {
                 ptx::tmem_ld_wait();                              // va = chunk c
+                stamp();                                          // chunk c in registers
                 ptx::tmem_ld_32x32(t_addr + (c + 1) * 32, vb);    // chunks is even: chunk c+1 exists
                 scale(va, c);
                 emit(va, c);
+                stamp();                                          // chunk c staged, store issued
                 ptx::tmem_ld_wait();                              // vb = chunk c+1
                 scale(vb, c + 1);
                 if (c + 2 < chunks) ptx::tmem_ld_32x32(t_addr + (c + 2) * 32, va);
                 else release_slot();
                 if (args.store_gap_ns) __nanosleep(args.store_gap_ns);
                 emit(vb, c + 1);
+                stamp();                                          // chunk c+1 staged, store issued
                 if (args.store_gap_ns && c + 2 < chunks) __nanosleep(args.store_gap_ns);
+            }
+            if (etrace) {
+                if (issuer) ptx::bulk_wait_group_read<0>();
+                stamp();                                          // last store has read its box
+                if (issuer) ptx::bulk_wait_group<0>();
+                stamp();                                          // all of this warp's stores are complete
             }
         }
         // the staging box must outlive the stores' reads of it; the writes themselves complete with the grid
