@@ -110,9 +110,16 @@ int b200fp8_gemm_rowcol_scaled(int m, int k, int n, const void* a, int a_dtype, 
  * (GEMM/src/cublas.cu:37-53 sets A/B/D scale pointers on the matmul descriptor;
  * GEMM/include/helper.h:59-66 carries the amax and scale slots):
  *
- *     t      = alpha * a_scale * b_scale * (A B^T) + beta * D + bias[n]
+ *     t      = act(alpha * a_scale * b_scale * a_row_scale[m] * b_row_scale[n] * (A B^T) + beta * D + bias[n])
  *     amax_d = max over the M x N result of |t|          (NaNs are ignored)
  *     D      = convert(d_scale * t)
+ *
+ * a_row_scale (M floats, one per row of A) and b_row_scale (N floats, one per row of
+ * B) are the per-row scales of row-wise quantised operands (cuBLASLt's outer-vector
+ * scaling mode); they multiply the per-tensor scalars.  act is one of
+ * B200FP8_ACT_* and follows the bias, like cuBLASLt's RELU_BIAS / GELU_BIAS
+ * epilogues; amax_d sees the activated value.  Scales that vary along K (blocks of 32
+ * or 128 elements of K) are not offered: they cannot be applied after the sum.
  *
  * d_dtype: any B200FP8_OUT_*.  8-bit outputs round to nearest even and saturate to
  * the largest finite value (448 for E4M3, 57344 for E5M2), as the toolkit's host
@@ -131,7 +138,19 @@ typedef struct b200fp8_epilogue {
     float* amax_d;
     const void* bias;
     int bias_dtype;
+    /* fields below: present when struct_bytes == sizeof(b200fp8_epilogue); a caller compiled against the shorter
+       struct (struct_bytes == B200FP8_EPILOGUE_V1_BYTES) gets no row scales and no activation */
+    int activation;            /* B200FP8_ACT_* */
+    const float* a_row_scale;  /* M values or NULL */
+    const float* b_row_scale;  /* N values or NULL */
 } b200fp8_epilogue;
+
+/* RELU keeps NaNs.  GELU_ERF = 0.5 t (1 + erf(t / sqrt 2)), GELU_TANH = 0.5 t (1 + tanh(sqrt(2/pi) (t + 0.044715 t^3))),
+   both by short branch-free FP32 formulas: within 2e-6 relative of the exact function for t >= 0 and within
+   1e-6 |t| absolute for t < 0 (where the exact value itself falls below that). */
+enum { B200FP8_ACT_NONE = 0, B200FP8_ACT_RELU = 1, B200FP8_ACT_GELU_ERF = 2, B200FP8_ACT_GELU_TANH = 3 };
+/* size of b200fp8_epilogue before `activation` was added (offset of that field) */
+#define B200FP8_EPILOGUE_V1_BYTES ((int)offsetof(b200fp8_epilogue, activation))
 
 int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b,
                                  int b_dtype, long long ldb, void* d, int d_dtype, long long ldd,

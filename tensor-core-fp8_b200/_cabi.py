@@ -73,7 +73,8 @@ class EpilogueDesc(ctypes.Structure):
     """b200fp8_epilogue of include/b200fp8.h."""
     _fields_ = [("struct_bytes", ctypes.c_int), ("alpha", ctypes.c_float), ("beta", ctypes.c_float),
                 ("a_scale", ctypes.c_void_p), ("b_scale", ctypes.c_void_p), ("d_scale", ctypes.c_void_p),
-                ("amax_d", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("bias_dtype", ctypes.c_int)]
+                ("amax_d", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("bias_dtype", ctypes.c_int),
+                ("activation", ctypes.c_int), ("a_row_scale", ctypes.c_void_p), ("b_row_scale", ctypes.c_void_p)]
 
 
 class B200Fp8Error(RuntimeError):

@@ -479,7 +479,10 @@ int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype
                                  int b_dtype, long long ldb, void* d, int d_dtype, long long ldd,
                                  const b200fp8_epilogue* ep, const b200fp8_options* options, void* stream) {
     if (options && options->struct_bytes != static_cast<int>(sizeof(b200fp8_options))) return cudaErrorInvalidValue;
-    if (!ep || ep->struct_bytes != static_cast<int>(sizeof(b200fp8_epilogue))) return cudaErrorInvalidValue;
+    if (!ep || (ep->struct_bytes != static_cast<int>(sizeof(b200fp8_epilogue)) && ep->struct_bytes != B200FP8_EPILOGUE_V1_BYTES))
+        return cudaErrorInvalidValue;
+    const bool extended = ep->struct_bytes == static_cast<int>(sizeof(b200fp8_epilogue));
+    if (extended && (ep->activation < B200FP8_ACT_NONE || ep->activation > B200FP8_ACT_GELU_TANH)) return cudaErrorInvalidValue;
     if (d_dtype < B200FP8_OUT_F32 || d_dtype > B200FP8_OUT_E5M2) return cudaErrorInvalidValue;
     if (ep->bias && (ep->bias_dtype < B200FP8_OUT_F32 || ep->bias_dtype > B200FP8_OUT_F16)) return cudaErrorInvalidValue;
     if (ep->bias && (reinterpret_cast<uintptr_t>(ep->bias) % out_dtype_bytes(ep->bias_dtype))) return cudaErrorInvalidValue;
@@ -495,6 +498,11 @@ int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype
     epi.amax = ep->amax_d;
     epi.bias = ep->bias;
     epi.bias_dtype = ep->bias_dtype;
+    if (extended) {
+        epi.activation = ep->activation;
+        epi.a_row_scale = ep->a_row_scale;
+        epi.b_row_scale = ep->b_row_scale;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (ep->amax_d) {                            // the kernel merges by atomic max: start from zero, stream-ordered
         cudaError_t e = cudaMemsetAsync(ep->amax_d, 0, sizeof(float), st);

@@ -57,11 +57,14 @@ struct SkinnyArgs {
 
 // one element of D (column n) under the extended epilogue; `amax` is the thread's running |t| maximum
 template <class Args>
-__device__ __forceinline__ void skinny_store_epi(const Args& args, float alpha, float dscale, long long idx, int n,
+__device__ __forceinline__ void skinny_store_epi(const Args& args, float alpha, float dscale, long long idx, int m, int n,
                                                  float acc, float& amax) {
+    if (args.epi.b_row_scale != nullptr) acc *= __ldg(args.epi.b_row_scale + n);
+    if (args.epi.a_row_scale != nullptr) alpha *= __ldg(args.epi.a_row_scale + m);
     float v = alpha * acc;
     if (args.epi.beta != 0.0f) v += args.epi.beta * load_out(args.C, idx, args.epi.out_dtype);
     if (args.epi.bias != nullptr) v += load_out(args.epi.bias, n, args.epi.bias_dtype);
+    v = activate(v, args.epi.activation);
     amax = fmaxf(amax, fabsf(v));
     store_out(args.C, idx, dscale * v, args.epi.out_dtype);
 }
@@ -307,10 +310,10 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap tmap_b,   // B[N][K],
                 float* dst = args.C + m * args.ldc + n;
                 if (args.epi.active) {
                     const long long idx = m * args.ldc + n;
-                    if (n < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx, n, acc.x, epi_amax);
-                    if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 1, n + 1, acc.y, epi_amax);
-                    if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 2, n + 2, acc.z, epi_amax);
-                    if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 3, n + 3, acc.w, epi_amax);
+                    if (n < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx, static_cast<int>(m), n, acc.x, epi_amax);
+                    if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 1, static_cast<int>(m), n + 1, acc.y, epi_amax);
+                    if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 2, static_cast<int>(m), n + 2, acc.z, epi_amax);
+                    if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 3, static_cast<int>(m), n + 3, acc.w, epi_amax);
                 } else if (args.vec_store && n + 3 < args.N) {
                     *reinterpret_cast<float4*>(dst) = acc;
                 } else {

@@ -449,10 +449,10 @@ gemm_fp8_skinny_streamk_kernel(const __grid_constant__ CUtensorMap tmap_b,   // 
                     const long long idx = static_cast<long long>(m) * args.ldc + n;
                     float* dst = args.C + idx;
                     if (args.epi.active) {
-                        if (n < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx, n, acc.x, epi_amax);
-                        if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 1, n + 1, acc.y, epi_amax);
-                        if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 2, n + 2, acc.z, epi_amax);
-                        if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 3, n + 3, acc.w, epi_amax);
+                        if (n < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx, m, n, acc.x, epi_amax);
+                        if (n + 1 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 1, m, n + 1, acc.y, epi_amax);
+                        if (n + 2 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 2, m, n + 2, acc.z, epi_amax);
+                        if (n + 3 < args.N) skinny_store_epi(args, epi_alpha, epi_dscale, idx + 3, m, n + 3, acc.w, epi_amax);
                     } else if (args.vec_store && n + 3 < args.N) {
                         *reinterpret_cast<float4*>(dst) = acc;
                     } else {

@@ -50,8 +50,10 @@
 namespace b200fp8 {
 
 // Extended epilogue:
-//     t = alpha * sa * sb * (A B^T) + beta * D + bias[n]        amax = max |t| over the valid part of D
-//     D = convert(sd * t)                                       D in FP32, BF16, FP16, E4M3 or E5M2
+//     t = act(alpha * sa * sb * ra[m] * rb[n] * (A B^T) + beta * D + bias[n])      amax = max |t| over the valid part of D
+//     D = convert(sd * t)                                                          D in FP32, BF16, FP16, E4M3 or E5M2
+// ra / rb are optional vectors of per-row scales of A (M values) and of B (N values): the "outer vector" scaling of
+// cuBLASLt; act is none, ReLU or GELU (erf or tanh form), applied after the bias as cuBLASLt's fused epilogues do
 // (the knobs of the reference's cuBLASLt comparator, GEMM/src/cublas.cu:37-53: alpha, beta, scale pointers;
 // 8-bit outputs are rounded to nearest even and saturate to the largest finite value, like the toolkit's
 // host conversions that the reference uses for its inputs).  The plain operator (alpha = 1, beta = 0, FP32)
@@ -66,7 +68,42 @@ struct Epilogue {
     float* amax;           // optional device float (zero at launch): receives max |t| by atomic max; NaNs are ignored
     const void* bias;      // optional device vector of N values added to every row
     int bias_dtype;        // 0 FP32, 1 BF16, 2 FP16
+    const float* a_row_scale;   // optional device vector of M factors, one per row of A (= row of D)
+    const float* b_row_scale;   // optional device vector of N factors, one per row of B (= column of D)
+    int activation;        // 0 none, 1 ReLU, 2 GELU 0.5 t (1 + erf(t / sqrt 2)), 3 GELU 0.5 t (1 + tanh(sqrt(2/pi) (t + 0.044715 t^3)))
 };
+
+// The activations.  Code size matters more than instruction count here: the tile kernels unroll the epilogue over 32
+// accumulator registers at three places, every instruction of it runs a handful of times per launch, and a one-tile
+// launch pays an instruction-cache miss for every line it touches (ReLU written as one branch of a per-element
+// switch next to an inlined erff doubled the time of 2048^3; erff behind a call cost 10 us there).  So: one loop per
+// activation, and branch-free formulas of a dozen instructions.
+__device__ __forceinline__ float relu(float t) { return t > 0.0f ? t : (t == t ? 0.0f : t); }   // a NaN stays a NaN
+// 0.5 t (1 + erf(t / sqrt 2)) with erf(x) = 1 - (a1 s + ... + a5 s^5) exp(-x^2), s = 1 / (1 + p x), x >= 0 (Abramowitz &
+// Stegun 7.1.26; in FP32 arithmetic |error of erf| < 7e-7).  1 + erf is formed without cancellation on either side:
+// the result is within 2e-6 relative for t >= 0 and within 1e-6 |t| absolute for t < 0.
+__device__ __forceinline__ float gelu_erf(float t) {
+    const float x = fabsf(t) * 0.70710678118654752f;
+    const float s = __fdividef(1.0f, fmaf(0.3275911f, x, 1.0f));
+    float p = fmaf(1.061405429f, s, -1.453152027f);
+    p = fmaf(p, s, 1.421413741f);
+    p = fmaf(p, s, -0.284496736f);
+    p = fmaf(p, s, 0.254829592f);
+    const float tail = p * s * __expf(-x * x);            // 1 - erf(|x|) = erfc(|x|)
+    return 0.5f * t * (t >= 0.0f ? 2.0f - tail : tail);   // 1 + erf(x): 2 - erfc(|x|) right of zero, erfc(|x|) left of it
+}
+// 0.5 t (1 + tanh u) = t / (1 + exp(-2u)), u = sqrt(2/pi) (t + 0.044715 t^3); ex2.approx and an approximate
+// division: same bounds, no branch, eight instructions
+__device__ __forceinline__ float gelu_tanh(float t) {
+    const float u2 = -1.5957691216057308f * t * fmaf(0.044715f * t, t, 1.0f);
+    return __fdividef(t, 1.0f + __expf(u2));
+}
+__device__ __forceinline__ float activate(float t, int activation) {
+    if (activation == 1) return relu(t);
+    if (activation == 2) return gelu_erf(t);
+    if (activation == 3) return gelu_tanh(t);
+    return t;
+}
 
 __host__ __device__ __forceinline__ int out_dtype_bytes(int out_dtype) {
     return out_dtype == 0 ? 4 : out_dtype <= 2 ? 2 : 1;
@@ -538,11 +575,11 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool issuer = ptx::elect_one();                    // this lane owns the warp's bulk-store groups
         const uint64_t store_policy = ptx::l2_policy(args.l2_stores);
         constexpr int kChunks = BN / 32 / (NACC == 1 ? 2 : 1);    // 32-column chunks this warp drains per tile
-        float epi_alpha = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
+        float epi_alpha0 = 1.0f, epi_dscale = 1.0f, epi_amax = 0.0f;
         if (args.epi.active) {
-            epi_alpha = args.epi.alpha;
-            if (args.epi.a_scale) epi_alpha *= *args.epi.a_scale;
-            if (args.epi.b_scale) epi_alpha *= *args.epi.b_scale;
+            epi_alpha0 = args.epi.alpha;
+            if (args.epi.a_scale) epi_alpha0 *= *args.epi.a_scale;
+            if (args.epi.b_scale) epi_alpha0 *= *args.epi.b_scale;
             if (args.epi.d_scale) epi_dscale = *args.epi.d_scale;
         }
         int it = 0;
@@ -574,6 +611,14 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!args.epi.active) return;
                 const int col0 = col_base + c * 32;
                 const int row = row0 + lane;
+                // per-column vectors: lane l fetches element col0 + l once (one coalesced load per warp and chunk), the
+                // values then travel by shuffle; columns beyond N get factor 1 / bias 0 and are never stored
+                if (args.epi.b_row_scale != nullptr) {
+                    const float mine = (col0 + lane < args.N) ? __ldg(args.epi.b_row_scale + col0 + lane) : 1.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__shfl_sync(0xffffffffu, mine, i) * __uint_as_float(v[i]));
+                }
+                const float epi_alpha = (args.epi.a_row_scale != nullptr && row < args.M) ? epi_alpha0 * __ldg(args.epi.a_row_scale + row) : epi_alpha0;
                 if (args.epi.beta != 0.0f && row < args.M) {
                     const long long base = static_cast<long long>(row) * args.ldc + col0;
 #pragma unroll
@@ -586,10 +631,19 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(epi_alpha * __uint_as_float(v[i]));
                 }
                 if (args.epi.bias != nullptr) {
+                    const float mine = (col0 + lane < args.N) ? load_out(args.epi.bias, col0 + lane, args.epi.bias_dtype) : 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col0 + i < args.N)
-                            v[i] = __float_as_uint(__uint_as_float(v[i]) + load_out(args.epi.bias, col0 + i, args.epi.bias_dtype));
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __shfl_sync(0xffffffffu, mine, i));
+                }
+                if (args.epi.activation == 1) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(relu(__uint_as_float(v[i])));
+                } else if (args.epi.activation == 2) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(gelu_erf(__uint_as_float(v[i])));
+                } else if (args.epi.activation == 3) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(gelu_tanh(__uint_as_float(v[i])));
                 }
                 if (args.epi.amax != nullptr && row < args.M) {
 #pragma unroll

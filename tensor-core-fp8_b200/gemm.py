@@ -138,12 +138,20 @@ def gemm_scaled(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: flo
 EPILOGUE_OUT_DTYPES = {**OUT_DTYPES, torch.float8_e4m3fn: 3, torch.float8_e5m2: 4}
 
 
+ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3}     # B200FP8_ACT_* of include/b200fp8.h
+
+
 def gemm_epilogue(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: float = 1.0, beta: float = 0.0,
                   a_scale: torch.Tensor | None = None, b_scale: torch.Tensor | None = None,
                   d_scale: torch.Tensor | None = None, amax_d: torch.Tensor | None = None,
-                  bias: torch.Tensor | None = None, depth: int = 0, kernel: int = KERNEL_AUTO, split_k: int = 0,
-                  max_ctas: int = 0):
-    """t = alpha * a_scale * b_scale * (A B^T) + beta * D + bias[n];  amax_d = max |t|;  D = convert(d_scale * t).
+                  bias: torch.Tensor | None = None, a_row_scale: torch.Tensor | None = None,
+                  b_row_scale: torch.Tensor | None = None, activation: str | int = 0, depth: int = 0,
+                  kernel: int = KERNEL_AUTO, split_k: int = 0, max_ctas: int = 0):
+    """t = act(alpha * a_scale * b_scale * a_row_scale[m] * b_row_scale[n] * (A B^T) + beta * D + bias[n]);
+    amax_d = max |t|;  D = convert(d_scale * t).
+
+    a_row_scale (M float32 values) and b_row_scale (N) are per-row scales of row-wise quantised operands;
+    activation is "none", "relu", "gelu" (erf form) or "gelu_tanh", applied after the bias.
 
     The whole epilogue of the reference's cuBLASLt comparator (GEMM/src/cublas.cu:37-53; amax and scale slots in
     GEMM/include/helper.h:59-66).  D may be float32, bfloat16, float16, float8_e4m3fn or float8_e5m2 (8-bit outputs
@@ -161,10 +169,21 @@ def gemm_epilogue(a: torch.Tensor, b: torch.Tensor, d: torch.Tensor, *, alpha: f
             raise TypeError("scales and amax are one-element float32 CUDA tensors")
     if bias is not None and (bias.dtype not in OUT_DTYPES or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous()):
         raise TypeError("bias is a contiguous CUDA vector of N float32 / bfloat16 / float16 values")
+    for v_, rows, what in ((a_row_scale, m, "a_row_scale has M"), (b_row_scale, n, "b_row_scale has N")):
+        if v_ is not None and (v_.dtype != torch.float32 or not v_.is_cuda or v_.numel() != rows or not v_.is_contiguous()
+                               or v_.device != d.device):
+            raise TypeError(f"{what} contiguous float32 values on the device of d")
+    if isinstance(activation, str):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"activation is one of {sorted(ACTIVATIONS)}")
+        activation = ACTIVATIONS[activation]
+    if activation not in ACTIVATIONS.values():
+        raise ValueError("unknown activation")
     _check_operands(m, k, n, a, b, d, a.stride(0) if m > 1 else k, b.stride(0) if n > 1 else k, d.stride(0) if m > 1 else n, "d")
     ptr = lambda t: t.data_ptr() if t is not None else None
     ep = _cabi.EpilogueDesc(ctypes.sizeof(_cabi.EpilogueDesc), float(alpha), float(beta), ptr(a_scale), ptr(b_scale),
-                            ptr(d_scale), ptr(amax_d), ptr(bias), OUT_DTYPES[bias.dtype] if bias is not None else 0)
+                            ptr(d_scale), ptr(amax_d), ptr(bias), OUT_DTYPES[bias.dtype] if bias is not None else 0,
+                            int(activation), ptr(a_row_scale), ptr(b_row_scale))
     opt = Options(ctypes.sizeof(Options), depth, kernel, split_k, max_ctas)
     with torch.cuda.device(d.device):
         rc = _cabi.lib().b200fp8_gemm_rowcol_epilogue(
