@@ -535,6 +535,77 @@ def reference_kernels_side(torch, g, dev):
     return out
 
 
+def fused_epilogue_side(torch, g, dev):
+    """The extended epilogue on the 8192^3 shape: FP32 plain store against BF16 output with per-row scales of A and
+    of B, bias and GELU (the epilogue of a row-wise quantised linear layer), each as a CUDA graph of 8 launches over two
+    B / D sets, three alternating rounds.  Parity of the timed BF16 buffer: sampled full rows against FP64
+    (tolerance of the operator scaled by the factors, widened by the activation's slope and BF16 rounding)."""
+    import numpy as np
+    from oracle import fp8_oracle as fo
+    M = K = N = 8192
+    iters, nsets = 8, 2
+    a = torch.empty((M, K), dtype=torch.float8_e4m3fn, device=dev)
+    g.fill_normal(a, 1.0, SEED_BASE + 700)
+    bs, c32, d16 = [], [], []
+    for i in range(nsets):
+        b = torch.empty((N, K), dtype=torch.float8_e4m3fn, device=dev)
+        g.fill_normal(b, 1.0, SEED_BASE + 701 + i)
+        bs.append(b)
+        c32.append(torch.empty((M, N), dtype=torch.float32, device=dev))
+        d16.append(torch.empty((M, N), dtype=torch.bfloat16, device=dev))
+    gen = torch.Generator(device=dev).manual_seed(SEED_BASE + 710)
+    ra = torch.rand(M, generator=gen, device=dev) * 0.02 + 0.001
+    rb = torch.rand(N, generator=gen, device=dev) * 0.02 + 0.001
+    bias = torch.randn(N, generator=gen, device=dev)
+
+    def graph_of(fn):
+        fn(0)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for i in range(iters):
+                fn(i)
+        return gr.replay
+
+    variants = {
+        "f32_plain": graph_of(lambda i: g.gemm_ex(a, bs[i % nsets], c32[i % nsets])),
+        "bf16_rowscales_bias_gelu_tanh": graph_of(lambda i: g.gemm_epilogue(
+            a, bs[i % nsets], d16[i % nsets], a_row_scale=ra, b_row_scale=rb, bias=bias, activation="gelu_tanh")),
+        "bf16_rowscales_bias_gelu_erf": graph_of(lambda i: g.gemm_epilogue(
+            a, bs[i % nsets], d16[i % nsets], a_row_scale=ra, b_row_scale=rb, bias=bias, activation="gelu")),
+    }
+    times = {k: [] for k in variants}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rnd in range(4):
+        for name, run in variants.items():
+            run()
+            e0.record()
+            run()
+            e1.record()
+            torch.cuda.synchronize()
+            if rnd:
+                times[name].append(e0.elapsed_time(e1) / iters)
+    out = {"shape": "8192^3 e4m3 x e4m3", "timing": f"CUDA graph of {iters} launches over {nsets} B / D sets, 3 alternating rounds",
+           "ms": {k: sum(v) / len(v) for k, v in times.items()}}
+    # parity of D buffer 0 as the last timed replay (erf form) left it
+    rng = np.random.default_rng(12)
+    pick = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, 6)]))
+    tm = torch.from_numpy(pick).to(dev)
+    C64, S = fo.gemm_f64(np.ascontiguousarray(a.view(torch.uint8)[tm].cpu().numpy()), 0, bs[0].view(torch.uint8).cpu().numpy(), 0)
+    f = ra[tm].cpu().numpy().astype(np.float64)[:, None] * rb.cpu().numpy().astype(np.float64)[None, :]
+    pre = f * C64 + bias.cpu().numpy().astype(np.float64)[None, :]
+    from math import sqrt
+    from scipy.special import erf
+    want = 0.5 * pre * (1.0 + erf(pre / sqrt(2.0)))
+    tol = 1.13 * (f * (1e-3 * S + 1e-6) + 2.0 ** -21 * (np.abs(pre) + np.abs(f * C64))) + 2e-6 * np.abs(pre) + 2.0 ** -8 * np.abs(want)
+    got = d16[0][tm].float().cpu().numpy().astype(np.float64)
+    ratio = np.abs(got - want) / tol
+    out["parity"] = {"worst": float(ratio.max()), "elements_outside_tolerance": int((ratio > 1).sum()),
+                     "sample": f"{len(pick)} full rows of the timed BF16 buffer against FP64 (scales, bias, GELU by erf)"}
+    out["device_status"] = g.device_status()
+    return out
+
+
 def run_sparse(args, g, torch, dev, json_fd):
     """GEMV / blocked-ELL SpMM / SpMV on one GPU: all steps in one CUDA graph over rotating operand sets larger than
     L2; FLOPs and bytes count the STORED blocks only (algorithmic work of the sparse problem)."""
@@ -1065,6 +1136,8 @@ def main() -> int:
             line["configs"] = {args.workload: measure_config(torch, g, cmp, dev, args.workload, M, K, N, code[args.a_dtype],
                                                              code[args.b_dtype], args.depth, args.kernel, peaks)}
         line["side"] = {"reference_kernels": reference_kernels_side(torch, g, dev)}
+        if args.workload == "shard32768":
+            line["side"]["fused_epilogue"] = fused_epilogue_side(torch, g, dev)
 
     # ---- the reference's CPU loop timed on this box's host cores (rank 0, N = 1 only) ----
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
