@@ -346,6 +346,19 @@ int b200fp8_ipc_free(void* device_ptr);
 /* Number of this library's kernels launched by the calling thread so far. */
 long long b200fp8_launch_count(void);
 
+/*
+ * How the current device's SMs divide over the two halves of its L2 (a B200 is two dies, each with half of the SMs
+ * and half of the L2; which SM ids sit on which die differs between GPUs).  The library measures this once per device,
+ * when the device is first used (two small kernels that time reads, a transient 16 MiB allocation), and gives the
+ * CTA pairs of each die a contiguous run of tiles in long persistent runs, so that operand panels cross the
+ * die-to-die link for one die instead of two.  B200FP8_DIE_AWARE=0 in the environment switches both off.
+ * mask (three 64-bit words, optional): bit s is set when SM s sits on the second side, the first side being the one
+ * the measuring CTA happened to run on.  Returns the number of SMs on the second side, or 0 (and an all-zero mask)
+ * when the split is not known: switched off, the measurement could not run, or it did not show two halves.
+ * No counterpart in the reference.
+ */
+int b200fp8_l2_sides(unsigned long long mask[3]);
+
 /* "b200fp8 <version> sm_100a" */
 const char* b200fp8_version(void);
 

@@ -54,6 +54,7 @@ DECLARED_SYMBOLS = (
     "b200fp8_ipc_close",
     "b200fp8_ipc_free",
     "b200fp8_launch_count",
+    "b200fp8_l2_sides",
     "b200fp8_version",
 )
 # the reference's operator API (GEMM/include/gemm.cuh:12-55) as the C++ linker sees it
@@ -132,6 +133,8 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_ipc_free.argtypes = [vp]
         L.b200fp8_device_status.argtypes = [ctypes.POINTER(ci), ci]
         L.b200fp8_launch_count.restype = ll
+        L.b200fp8_l2_sides.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
+        L.b200fp8_l2_sides.restype = ctypes.c_int
         L.b200fp8_version.restype = ctypes.c_char_p
         _lib = L
     return _lib

@@ -15,19 +15,24 @@
 #include "gemm_skinny_sm100.cuh"
 #include "gemm_skinny_streamk_sm100.cuh"
 #include "fill_fp8.cuh"
+#include "l2_sides.cuh"
 
 namespace b200fp8 {
 namespace {
 
 constexpr int kMaxDevices = 64;
 constexpr int kPaceSlots = 256;
+constexpr int kPaceWords = 4;
 
 struct DeviceCtx {
     bool ready = false;
     int sm_count = 0;
     int* status = nullptr;          // device status word
-    unsigned int* pace = nullptr;   // ring of tile-pacing counters, one per launch in flight
+    unsigned int* pace = nullptr;   // ring of launch scratch slots, one per launch in flight: kPaceWords zeroed words
+                                    // (word 0 the tile-pacing counter, words 1 and 2 the start-position tickets)
     unsigned int pace_next = 0;
+    bool sides_known = false;       // side_mask holds a measured split of the SMs over the two halves of the L2
+    uint64_t side_mask[3] = {0, 0, 0};
     // buffers of the host-pointer entry point
     void* host_a = nullptr; size_t host_a_bytes = 0;
     void* host_b = nullptr; size_t host_b_bytes = 0;
@@ -72,7 +77,10 @@ cudaError_t get_ctx(DeviceCtx** out) {
         if ((e = load_encode()) != cudaSuccess) return e;
         if ((e = cudaMalloc(&c.status, sizeof(int))) != cudaSuccess) return e;
         if ((e = cudaMemset(c.status, 0, sizeof(int))) != cudaSuccess) return e;
-        if ((e = cudaMalloc(&c.pace, kPaceSlots * sizeof(unsigned int))) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&c.pace, kPaceSlots * kPaceWords * sizeof(unsigned int))) != cudaSuccess) return e;
+        const char* die_aware = getenv("B200FP8_DIE_AWARE");     // 0: schedule as if the L2 were one piece
+        c.sides_known = (!die_aware || atoi(die_aware) != 0) && measure_l2_sides(c.sm_count, c.side_mask);
+        (void)cudaGetLastError();   // a measurement that could not run is not an error of the caller
         c.ready = true;
     }
     *out = &c;
@@ -283,11 +291,15 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
         unsigned int* slot;
         {
             std::lock_guard<std::mutex> lock(g_mutex);
-            slot = ctx.pace + (ctx.pace_next++ % kPaceSlots);
+            slot = ctx.pace + kPaceWords * (ctx.pace_next++ % kPaceSlots);
         }
-        if ((e = cudaMemsetAsync(slot, 0, sizeof(unsigned int), stream)) != cudaSuccess) return e;
+        if ((e = cudaMemsetAsync(slot, 0, kPaceWords * sizeof(unsigned int), stream)) != cudaSuccess) return e;
         args.pace = slot;
         args.pace_limit_ns = static_cast<unsigned int>(tune().pace_limit_ns);
+        if (ctx.sides_known && units * CTAS == ctx.sm_count) {   // every SM holds exactly one CTA: the tickets of the two sides cannot collide
+            args.tickets = slot + 1;
+            for (int i = 0; i < 3; ++i) args.side_mask[i] = ctx.side_mask[i];
+        }
     }
 
     cudaLaunchConfig_t cfg{};
@@ -908,6 +920,18 @@ int b200fp8_ipc_close(void* device_ptr) { return device_ptr ? cudaIpcCloseMemHan
 int b200fp8_ipc_free(void* device_ptr) { return device_ptr ? cudaFree(device_ptr) : cudaSuccess; }
 
 long long b200fp8_launch_count(void) { return t_launches; }
+
+int b200fp8_l2_sides(unsigned long long mask[3]) {
+    DeviceCtx* ctx = nullptr;
+    if (mask) mask[0] = mask[1] = mask[2] = 0;
+    if (get_ctx(&ctx) != cudaSuccess || !ctx->sides_known) return 0;
+    int count = 0;
+    for (int i = 0; i < 3; ++i) {
+        if (mask) mask[i] = ctx->side_mask[i];
+        count += __builtin_popcountll(ctx->side_mask[i]);
+    }
+    return count;
+}
 
 #ifdef B200FP8_DIAGNOSTICS
 // diagnostics build only (declared in include/b200fp8.h under the same macro)

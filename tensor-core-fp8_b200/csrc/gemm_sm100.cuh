@@ -180,6 +180,13 @@ struct GemmArgs {
     int* status;          // device status word: 0 = ok, else first error code recorded
     unsigned int* pace;   // tile-pacing counter (zero at launch) or nullptr: see the producer warp
     unsigned int pace_limit_ns;
+    // Die-aware start positions (nullptr = off).  side_mask: bit s set = SM s sits at the second half of the L2;
+    // tickets[0 / 1]: zero at launch.  CTAs (pairs) on the first side take start positions 0, 1, 2, ... of the
+    // persistent walk, those on the second side tile_step - 1, tile_step - 2, ...: within every round of the walk
+    // each die then works on its own contiguous run of tiles, i.e. on its own B panels, which cross the die-to-die
+    // fabric for one die instead of two.
+    unsigned int* tickets;
+    unsigned long long side_mask[3];
     unsigned int store_gap_ns;   // pause between an epilogue warp's chunk stores (spreads C writes over the next main loop)
     long long* trace;     // diagnostics (debug & 64): per k-block clock64 stamps of CTA 0's MMA thread
     // Fused all-gather of C (N-sharded multi-GPU run): every finished box is also stored, with plain
@@ -336,8 +343,27 @@ gemm_fp8_rowcol_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     // persistent walk over work items, identical in every role
     const int num_items = args.full_items + 2 * args.split_tiles;
-    const int first_tile = blockIdx.x / CTAS;
     const int tile_step = gridDim.x / CTAS;
+    int first_tile = blockIdx.x / CTAS;
+    if (args.tickets != nullptr) {
+        volatile int* ticket_slot = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff + 4);
+        if (rank == 0 && threadIdx.x == 0) {
+            const unsigned int smid = ptx::smid();
+            const unsigned int side = smid < 192u ? static_cast<unsigned int>((args.side_mask[smid >> 6] >> (smid & 63u)) & 1ull) : 0u;
+            const int drawn = static_cast<int>(atomicAdd(args.tickets + side, 1u));
+            const int pos = side ? tile_step - 1 - drawn : drawn;
+            *ticket_slot = (pos >= 0 && pos < tile_step) ? pos : first_tile;
+        }
+        __syncwarp();
+        if (pair) {
+            ptx::cluster_arrive();                        // release / acquire: the leader's slot is visible to its peer
+            ptx::cluster_wait();
+            first_tile = rank == 0 ? *ticket_slot : static_cast<int>(ptx::ld_shared_cluster_u32(ptx::mapa(smem_base + L::kAbortOff + 4, 0)));
+        } else {
+            __syncthreads();
+            first_tile = *ticket_slot;
+        }
+    }
     const int nkb = args.num_k_blocks;
     // k-blocks this CTA streams over all of its work items: the last stage of the stream may hold fewer than KPS
     const long long stream_kb = first_tile < num_items

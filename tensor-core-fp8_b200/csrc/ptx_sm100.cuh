@@ -41,6 +41,19 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
     return r;
 }
 
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+    uint32_t v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
+// id of the SM this thread runs on
+__device__ __forceinline__ uint32_t smid() {
+    uint32_t v;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(v));
+    return v;
+}
+
 __device__ __forceinline__ void cluster_arrive() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }

@@ -1,0 +1,79 @@
+"""The split of the SMs over the two halves of the L2 and the die-aware start positions of long persistent runs.
+
+A B200 is two dies, each with half of the SMs and half of the L2; the library measures which SM sits where (reads of
+lines whose home is on the other die take about twice as long) and, in launches of eight or more rounds of tiles, lets
+the CTA pairs of each die draw start positions from opposite ends of the walk.  The schedule decides only which CTA
+computes which tile: every element of C must be the same bit pattern with the feature on and off.  (No counterpart in
+the reference, whose kernels are not persistent: GEMM/src/gemm.cu:263-277 launches one CTA per tile.)
+"""
+import ctypes
+import hashlib
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from __graft_entry__ import load_package
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+CHILD = r"""
+import sys, hashlib
+sys.path.insert(0, %r)
+import torch
+from __graft_entry__ import load_package
+pkg = load_package(); g = pkg.gemm
+torch.cuda.set_device(0)
+print("sides", pkg._cabi.lib().b200fp8_l2_sides(None))
+for kernel, (m, k, n) in ((3, (8192, 512, 8192)), (5, (8192, 256, 16384))):
+    a = torch.empty((m, k), dtype=torch.float8_e4m3fn, device="cuda"); g.fill_normal(a, 1.0, 71)
+    b = torch.empty((n, k), dtype=torch.float8_e5m2, device="cuda"); g.fill_normal(b, 2.0, 72)
+    c = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    g.gemm_ex(a, b, c, kernel=kernel)
+    torch.cuda.synchronize()
+    assert g.device_status() == 0
+    print("hash", kernel, hashlib.sha256(c.cpu().numpy().tobytes()).hexdigest())
+"""
+
+
+def run_child(die_aware: str):
+    env = dict(os.environ, B200FP8_DIE_AWARE=die_aware)
+    res = subprocess.run([sys.executable, "-c", CHILD % ROOT], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    lines = res.stdout.strip().splitlines()
+    sides = int([ln for ln in lines if ln.startswith("sides")][0].split()[1])
+    return sides, [ln for ln in lines if ln.startswith("hash")]
+
+
+def test_measured_split_is_two_halves():
+    assert torch.cuda.is_available()
+    pkg = load_package()
+    lib = pkg._cabi.lib()
+    torch.cuda.set_device(0)
+    mask = (ctypes.c_ulonglong * 3)()
+    count = lib.b200fp8_l2_sides(mask)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if os.environ.get("B200FP8_DIE_AWARE") == "0":
+        assert count == 0 and not any(mask)
+        return
+    assert count == sum(bin(w).count("1") for w in mask)
+    assert 0.4 * sms <= count <= 0.6 * sms, (count, sms)   # two dies with about the same number of SMs (74 + 74 seen)
+    assert all(not (mask[s // 64] >> (s % 64)) & 1 for s in range(sms, 192))
+    # the two SMs of a TPC (ids 2i, 2i + 1) sit on the same die: CTA pairs never straddle the split
+    for s in range(0, sms - 1, 2):
+        assert ((mask[s // 64] >> (s % 64)) & 1) == ((mask[(s + 1) // 64] >> ((s + 1) % 64)) & 1), s
+    assert lib.b200fp8_l2_sides(None) == count           # repeated query: measured once, same answer
+
+
+def test_results_do_not_depend_on_the_start_positions():
+    """Thirteen and more rounds of tiles per CTA pair (tile pacing and tickets active) on the 256 x 256 and the
+    256 x 512 pair kernels: bitwise the same C with the die-aware start positions and without."""
+    assert torch.cuda.is_available()
+    sides_on, on = run_child("1")
+    sides_off, off = run_child("0")
+    assert sides_off == 0
+    assert sides_on > 0
+    assert len(on) == 2 and on == off
