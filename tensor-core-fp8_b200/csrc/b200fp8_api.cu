@@ -364,8 +364,13 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else if (m <= kSkinnyMaxM && m >= 32 && k <= 2048 && (n + 63) / 64 <= ctx->sm_count)
             kernel = 2 * n128_cols <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
         else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
-        // long runs are power-limited: the wide tile moves a quarter less data per flop
-        else if (wide_tiles >= 16LL * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N512;
+        // Long runs are power-limited and the wide tile moves a quarter less data per flop, but it has no second
+        // accumulator slot, so its epilogue (about 5 us) is exposed once per tile: it pays when a tile's main loop
+        // is long.  Measured against the 256 x 256 pair tile: K = 32768 wins 5-8 % from 7 rounds of tiles on
+        // (32768 x 32768 x 2048..8192, 8192 x 32768 x 8192); K = 16384 wins 3 % at 14 rounds (16384 x 16384 x 8192) and
+        // loses 4-9 % at 7-10 rounds; K = 8192 loses 4-15 % everywhere (8192 x 8192 x 28672: 1580 against 1435 us).
+        else if ((k >= 32768 && wide_tiles >= 4LL * (ctx->sm_count / 2)) || (k >= 16384 && wide_tiles >= 13LL * (ctx->sm_count / 2)))
+            kernel = B200FP8_KERNEL_PAIR_N512;
         else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
         // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
         // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
