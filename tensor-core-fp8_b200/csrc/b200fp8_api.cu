@@ -371,6 +371,11 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // loses 4-9 % at 7-10 rounds; K = 8192 loses 4-15 % everywhere (8192 x 8192 x 28672: 1580 against 1435 us).
         else if ((k >= 32768 && wide_tiles >= 4LL * (ctx->sm_count / 2)) || (k >= 16384 && wide_tiles >= 13LL * (ctx->sm_count / 2)))
             kernel = B200FP8_KERNEL_PAIR_N512;
+        // a short K makes the step a store of C with some arithmetic attached: one-CTA 128 x 256 tiles drain their
+        // accumulators from twice as many independent CTAs as the pairs do (4096 x 512 x 4096: 15.9 against 18.7 us,
+        // 8192 x 512 x 8192: 55 against 75-78, 8192 x 1024 x 8192: 81-84 against 92-93, 2304 x 1024 x 2304: 10.5 against 12.0;
+        // at K = 1536 and 2048 the pair tile leads again)
+        else if (k <= 1024 && n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
         else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
         // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
         // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
