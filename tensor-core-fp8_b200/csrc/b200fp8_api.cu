@@ -364,6 +364,10 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else if (m <= kSkinnyMaxM && m >= 32 && k <= 2048 && (n + 63) / 64 <= ctx->sm_count)
             kernel = 2 * n128_cols <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
         else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
+        // at most 128 columns: tiles of 256 columns would compute padding for half of their width
+        // (16384 x 4096 x 128: 11.7 us with 128 x 128 tiles against 16.2-16.5 with the 256-wide ones)
+        else if (n <= 128)
+            kernel = 2 * static_cast<long long>((m + 127) / 128) <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
         // Long runs are power-limited and the wide tile moves a quarter less data per flop, but it has no second
         // accumulator slot, so its epilogue (about 5 us) is exposed once per tile: it pays when a tile's main loop
         // is long.  Measured against the 256 x 256 pair tile: K = 32768 wins 5-8 % from 7 rounds of tiles on
@@ -376,7 +380,19 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // 8192 x 512 x 8192: 55 against 75-78, 8192 x 1024 x 8192: 81-84 against 92-93, 2304 x 1024 x 2304: 10.5 against 12.0;
         // at K = 1536 and 2048 the pair tile leads again)
         else if (k <= 1024 && n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
-        else if (pair_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_PAIR_N256;
+        else if (pair_tiles >= ctx->sm_count / 2) {
+            kernel = B200FP8_KERNEL_PAIR_N256;
+            // few rounds: count them.  A last round of at most half the pairs costs half a round (it runs as
+            // half-width items); the one-CTA tile is about a tenth slower per round but its rounds hold twice as many
+            // tiles of half the height (1152 x 8192 x 4096: 80 pair tiles = 1.5 rounds, 144 one-CTA tiles = 1: 33.0 against 38.8 us)
+            const long long pairs = ctx->sm_count / 2;
+            if (pair_tiles < 4 * pairs) {
+                const long long rem = pair_tiles % pairs;
+                const double rounds_pair = static_cast<double>(pair_tiles / pairs) + (rem == 0 ? 0.0 : 2 * rem <= pairs ? 0.5 : 1.0);
+                const double rounds_single = static_cast<double>((n256_tiles + ctx->sm_count - 1) / ctx->sm_count);
+                if (1.1 * rounds_single < rounds_pair) kernel = B200FP8_KERNEL_CTA1_N256;
+            }
+        }
         // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
         // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
         else if (4 * pair_tiles >= 3 * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N256;
@@ -384,7 +400,13 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // 128 x 128 tiles (measured at M = 130..256, N = K = 8192: 5-7 %)
         else if (m <= 256 && k >= 8192 && 4 * n128_cols >= 3 * (ctx->sm_count / 2) && n128_cols <= ctx->sm_count / 2)
             kernel = B200FP8_KERNEL_PAIR_N128;
-        else if (n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
+        // ... and the same for one or two columns of tiles under a tall A (8192 x 8192 x 136..256: 16.3-17.9 against 17.4-18.7 us)
+        else if (n > 128 && n <= 256 && k >= 8192 && 8LL * ((m + 255) / 256) >= 3 * (ctx->sm_count / 2) && 2LL * ((m + 255) / 256) <= ctx->sm_count / 2)
+            kernel = B200FP8_KERNEL_PAIR_N128;
+        // one round either way: with K >= 4096 the pair's shared B (32 instead of 48 KiB per CTA and k-block) wins 2-6 %
+        // (640 x 5120 x 5120, 200 x 4096 x 11008, 1024 x 4096 x 4096, 8192 x 8192 x 512); with a shorter K the one-CTA tile does
+        else if (n256_tiles >= ctx->sm_count / 2)
+            kernel = (k >= 4096 && 2 * pair_tiles <= ctx->sm_count) ? B200FP8_KERNEL_PAIR_N256 : B200FP8_KERNEL_CTA1_N256;
         // a problem of so few 128 x 128 tiles that twice as many 128 x 64 tiles still fit in one round: half the
         // main loop and half the epilogue per CTA (1024^3: 6.4 -> 5.5 us, 256^3: 5.2 -> 4.2 us)
         else if (2 * static_cast<long long>((m + 127) / 128) * n128_cols <= ctx->sm_count) kernel = B200FP8_KERNEL_CTA1_N64;
