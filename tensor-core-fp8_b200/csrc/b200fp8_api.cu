@@ -371,9 +371,10 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         // Long runs are power-limited and the wide tile moves a quarter less data per flop, but it has no second
         // accumulator slot, so its epilogue (about 5 us) is exposed once per tile: it pays when a tile's main loop
         // is long.  Measured against the 256 x 256 pair tile: K = 32768 wins 5-8 % from 7 rounds of tiles on
-        // (32768 x 32768 x 2048..8192, 8192 x 32768 x 8192); K = 16384 wins 3 % at 14 rounds (16384 x 16384 x 8192) and
-        // loses 4-9 % at 7-10 rounds; K = 8192 loses 4-15 % everywhere (8192 x 8192 x 28672: 1580 against 1435 us).
-        else if ((k >= 32768 && wide_tiles >= 4LL * (ctx->sm_count / 2)) || (k >= 16384 && wide_tiles >= 13LL * (ctx->sm_count / 2)))
+        // (32768 x 32768 x 2048..8192, 8192 x 32768 x 8192), K = 28672 5 % (8192 x 28672 x 8192; at 3.5 rounds it loses
+        // 7 %), K = 24576 ties, K = 20480 loses; K = 16384 wins 3 % at 14 rounds (16384 x 16384 x 8192) and loses 4-9 %
+        // at 7-10 rounds; K = 8192 loses 4-15 % everywhere (8192 x 8192 x 28672: 1580 against 1435 us).
+        else if ((k >= 28672 && wide_tiles >= 4LL * (ctx->sm_count / 2)) || (k >= 16384 && wide_tiles >= 13LL * (ctx->sm_count / 2)))
             kernel = B200FP8_KERNEL_PAIR_N512;
         // a short K makes the step a store of C with some arithmetic attached: one-CTA 128 x 256 tiles drain their
         // accumulators from twice as many independent CTAs as the pairs do (4096 x 512 x 4096: 15.9 against 18.7 us,
