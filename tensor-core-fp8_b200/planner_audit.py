@@ -8,7 +8,8 @@ The reference has one kernel per operator and nothing to choose (GEMM/src/gemm.c
 measured on one kind of GPU.  Run this after changing a rule or on a different part.  Protocol: each (shape, kernel)
 as a CUDA graph of back-to-back launches over rotating B / C buffers larger than L2 (shapes of more than 2 TFLOP
 launch by launch), the kernels of a shape timed in turn five times in shuffled order, every turn after a lead-in of
-the same kernel (one replay; 50 ms for the long shapes, whose clocks are set by the power cap), the median turn counted.  M <= 128 shapes also time the split-K kernels
+the same history (the AUTO kernel for one replay, or 50 ms for the long shapes whose clocks the power cap sets, then
+one untimed replay of the kernel itself), the median turn counted.  M <= 128 shapes also time the split-K kernels
 (ids 4 and 8).  Exit code 1 when a shape exceeds the threshold.
 """
 from __future__ import annotations
@@ -88,20 +89,22 @@ def time_shape(torch, g, m, k, n, kernels, rounds=5):
     long_steps = flops >= 2e12
     rng = random.Random(m * 1000003 + k * 1009 + n)
     order = list(runners)
+    common = runners[kernels[0]] if kernels[0] in runners else next(iter(runners.values()))
     for _ in range(rounds):
-        rng.shuffle(order)                               # no kernel keeps the same predecessor
+        rng.shuffle(order)
         for kernel in order:
-            # lead-in: one replay for short steps; for long ones 50 ms of this kernel alone, so that clocks and power
-            # are its own steady state and not what its predecessor left (an inefficient kernel leaves headroom)
+            # the same history before every timed replay, whatever ran before in the shuffled order: the first kernel
+            # of the list (AUTO) for a while (one replay; 50 ms for long steps, whose clocks the power cap sets), then
+            # one untimed replay of the kernel itself.  Without it a kernel timed after an inefficient one inherits
+            # that one's power headroom and reads up to a tenth faster.
             lead.record()
-            busy_ms = 0.0
             while True:
-                runners[kernel]()
+                common()
                 e0.record()
                 torch.cuda.synchronize()
-                busy_ms = lead.elapsed_time(e0)
-                if not long_steps or busy_ms >= 50.0:
+                if not long_steps or lead.elapsed_time(e0) >= 50.0:
                     break
+            runners[kernel]()
             e0.record()
             runners[kernel]()
             e1.record()
