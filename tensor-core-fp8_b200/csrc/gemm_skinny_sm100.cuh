@@ -377,11 +377,33 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
         // clusters of 8 CTAs pack badly into the GPCs: with more than 8 of them some wait for a second round
         // (K = 8192, N = 2048: M = 128 17 us with 8 splits, 10.8 us with 4; M = 16 11.8 us against 7.6 us)
         if (s > 4 && n_tiles > 8) s = 4;
+        // a split wants k-blocks of its own: with too few, the reduce-scatter of one more partial tile costs more than
+        // the shorter stream saves.  Eight for M >= 64, whose partial tiles are large (128 x 4096 x 1024: 6.8 us with 4
+        // splits against 7.4 with 8); four for smaller M once there are N tiles enough to occupy the GPU anyway
+        // (16 x 1024 x 4096: 3.7 us with 2 against 4.0 with 4; with 8-16 N tiles more splits still win: 1 x 2048 x 2048
+        // 3.5 us with 4 against 4.0 with 2)
+        if (mp >= 64 || n_tiles >= 32) {
+            const int own = mp >= 64 ? 8 : 4;
+            const int by_k = kb_total / own > 2 ? kb_total / own : 2;
+            if (s > by_k) s = by_k;
+        }
     }
     if (s > kSkinnyMaxSplits) s = kSkinnyMaxSplits;
     if (s > kb_total) s = kb_total;
     int per = (kb_total + s - 1) / s;
     s = (kb_total + per - 1) / per;          // no empty split
+    if (split_k <= 0) {
+        // the planner's own choice is a power of two: clusters of 3, 5, 6 or 7 CTAs place badly
+        // (16 x 1536 x 6144: 7.8 us with 3 splits against 4.7 with 2 or 4)
+        while (s & (s - 1)) {
+            int p = 1;
+            while (2 * p <= s) p *= 2;
+            per = (kb_total + p - 1) / p;
+            s = (kb_total + per - 1) / per;
+            if (s & (s - 1)) --s;            // e.g. 9 k-blocks: 4 splits of 3 leave 3 splits; go on from 2
+        }
+        per = (kb_total + s - 1) / s;
+    }
     *splits = s;
     *kb_per_split = per;
     int st = depth;
