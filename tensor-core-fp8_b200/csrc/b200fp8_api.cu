@@ -360,8 +360,11 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         if (ell) kernel = n256_tiles >= ctx->sm_count / 2 ? B200FP8_KERNEL_CTA1_N256 : B200FP8_KERNEL_CTA1_N128;
         // M <= 128: the split-K kernel streams a big B from HBM with every SM; with a short K and at most one round of
         // 128 x 64 tiles there is nothing to split and its reduce-scatter only costs (128 x 2048 x 2048: 12.7 us
-        // against 6.7 us for the tile kernel), so those go to the tile kernels unless M is tiny
-        else if (m <= kSkinnyMaxM && m >= 32 && k <= 2048 && (n + 63) / 64 <= ctx->sm_count)
+        // against 6.7 us for the tile kernel), so those go to the tile kernels: K <= 2048 for M > 64, K <= 1024 for
+        // 32 < M <= 64 (64 x 2048 x 4096: 5.5 us split in two against 5.9; 64 x 512 x 8192: 3.9 against 5.1 the other way),
+        // K <= 512 for 16 < M <= 32 (32 x 512 x 8192: 3.7 against 4.3; but 32 x 1024 x 2048: 3.9 against 4.1 the other way),
+        // never for M <= 16 (16 x 512 x 2048: 3.3 against 3.5)
+        else if (m <= kSkinnyMaxM && m > 16 && k <= (m > 64 ? 2048 : m > 32 ? 1024 : 512) && (n + 63) / 64 <= ctx->sm_count)
             kernel = 2 * n128_cols <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
         else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
         // at most 128 columns: tiles of 256 columns would compute padding for half of their width

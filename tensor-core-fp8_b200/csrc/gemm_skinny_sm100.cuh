@@ -378,13 +378,14 @@ inline void skinny_plan(int sm_count, int n, int k, int mp, int depth, int split
         // (K = 8192, N = 2048: M = 128 17 us with 8 splits, 10.8 us with 4; M = 16 11.8 us against 7.6 us)
         if (s > 4 && n_tiles > 8) s = 4;
         // a split wants k-blocks of its own: with too few, the reduce-scatter of one more partial tile costs more than
-        // the shorter stream saves.  Eight for M >= 64, whose partial tiles are large (128 x 4096 x 1024: 6.8 us with 4
+        // the shorter stream saves.  Eight for M > 64, whose partial tiles are large (128 x 4096 x 1024: 6.8 us with 4
         // splits against 7.4 with 8); four for smaller M once there are N tiles enough to occupy the GPU anyway
         // (16 x 1024 x 4096: 3.7 us with 2 against 4.0 with 4; with 8-16 N tiles more splits still win: 1 x 2048 x 2048
-        // 3.5 us with 4 against 4.0 with 2)
-        if (mp >= 64 || n_tiles >= 32) {
-            const int own = mp >= 64 ? 8 : 4;
-            const int by_k = kb_total / own > 2 ? kb_total / own : 2;
+        // 3.5 us with 4 against 4.0 with 2, 48 x 2048 x 2048 4.5 with 4 against 5.2 with 2)
+        if (mp > 64 || n_tiles >= 32) {
+            const int own = mp > 64 ? 8 : 4;
+            int by_k = 2;
+            while (2 * kb_total >= 3 * by_k * own) by_k *= 2;      // kb_total / own rounded to the nearest power of two
             if (s > by_k) s = by_k;
         }
     }

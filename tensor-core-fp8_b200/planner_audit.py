@@ -33,6 +33,7 @@ DEFAULT_SHAPES = """
 8192x8192x512 8192x8192x1024 16384x4096x128 4096x4096x384 640x5120x5120 1280x4096x12288 200x4096x11008
 1152x8192x4096 1152x4096x8192 1536x6144x1536 4096x11008x4096 8192x8192x28672 8192x28672x8192 8192x16384x12288
 16384x16384x8192 8192x32768x8192 32768x32768x4096 16x8192x8192 64x8192x8192 128x8192x8192 128x2048x2048
+32x512x8192 32x2048x8192 64x2048x4096 64x512x8192 48x2048x2048 128x4096x1024 16x1024x4096 1x2048x2048 32x8192x57344
 """.split()
 
 TILE_KERNELS = (1, 2, 3, 5, 6, 7)
