@@ -369,8 +369,11 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
         else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
         // at most 128 columns: tiles of 256 columns would compute padding for half of their width
         // (16384 x 4096 x 128: 11.7 us with 128 x 128 tiles against 16.2-16.5 with the 256-wide ones)
+        // one round of 256 x 128 pair tiles is level with or ahead of one round of 128 x 128 tiles (12.6 against 14.0-15.0 us on one box, 11.8 both on another)
         else if (n <= 128)
-            kernel = 2 * static_cast<long long>((m + 127) / 128) <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
+            kernel = 2 * static_cast<long long>((m + 127) / 128) <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64
+                     : (m + 255) / 256 <= ctx->sm_count / 2                        ? B200FP8_KERNEL_PAIR_N128
+                                                                                   : B200FP8_KERNEL_CTA1_N128;
         // Long runs are power-limited and the wide tile moves a quarter less data per flop, but it has no second
         // accumulator slot, so its epilogue (about 5 us) is exposed once per tile: it pays when a tile's main loop
         // is long.  Measured against the 256 x 256 pair tile: K = 32768 wins 5-8 % from 7 rounds of tiles on
