@@ -347,6 +347,14 @@ int b200fp8_ipc_free(void* device_ptr);
 long long b200fp8_launch_count(void);
 
 /*
+ * The kernel (a B200FP8_KERNEL_* id, never AUTO) that `kernel = AUTO` selects on the current device for a dense
+ * M x K x N problem; -1 for an invalid shape or when the device cannot be used.  For tools that audit the rules
+ * (time the selected kernel against the others) and for callers that want to log the choice.  No counterpart in the
+ * reference, which has one kernel per operator.
+ */
+int b200fp8_choose_kernel(int m, int k, int n);
+
+/*
  * How the current device's SMs divide over the two halves of its L2 (a B200 is two dies, each with half of the SMs
  * and half of the L2; which SM ids sit on which die differs between GPUs).  The library measures this once per device,
  * when the device is first used (two small kernels that time reads, a transient 16 MiB allocation), and gives the

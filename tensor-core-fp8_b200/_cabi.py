@@ -55,6 +55,7 @@ DECLARED_SYMBOLS = (
     "b200fp8_ipc_free",
     "b200fp8_launch_count",
     "b200fp8_l2_sides",
+    "b200fp8_choose_kernel",
     "b200fp8_version",
 )
 # the reference's operator API (GEMM/include/gemm.cuh:12-55) as the C++ linker sees it
@@ -135,6 +136,8 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_launch_count.restype = ll
         L.b200fp8_l2_sides.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
         L.b200fp8_l2_sides.restype = ctypes.c_int
+        L.b200fp8_choose_kernel.argtypes = [ci, ci, ci]
+        L.b200fp8_choose_kernel.restype = ci
         L.b200fp8_version.restype = ctypes.c_char_p
         _lib = L
     return _lib

@@ -321,6 +321,79 @@ cudaError_t launch_main(DeviceCtx& ctx, int m, int k, int n, const void* a, long
 
 bool valid_dtype(int d) { return d == B200FP8_E4M3 || d == B200FP8_E5M2; }
 
+// The automatic choice among the kernels for an M x K x N problem (sparse: blocked-ELL A).  Every rule carries the
+// measurement that decided it; `planner_audit.py` checks the whole table against forced kernels.
+int choose_kernel(int sm_count, int m, int k, int n, bool ell) {
+    int kernel = B200FP8_KERNEL_AUTO;
+    const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
+    const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
+    const long long wide_tiles = static_cast<long long>((m + 255) / 256) * ((n + 511) / 512);
+    const long long n128_cols = (n + 127) / 128;
+    if (ell) kernel = n256_tiles >= sm_count / 2 ? B200FP8_KERNEL_CTA1_N256 : B200FP8_KERNEL_CTA1_N128;
+    // M <= 128: the split-K kernel streams a big B from HBM with every SM; with a short K and at most one round of
+    // 128 x 64 tiles there is nothing to split and its reduce-scatter only costs (128 x 2048 x 2048: 12.7 us
+    // against 6.7 us for the tile kernel), so those go to the tile kernels: K <= 2048 for M > 64, K <= 1024 for
+    // 32 < M <= 64 (64 x 2048 x 4096: 5.5 us split in two against 5.9; 64 x 512 x 8192: 3.9 against 5.1 the other way),
+    // K <= 512 for 16 < M <= 32 (32 x 512 x 8192: 3.7 against 4.3; but 32 x 1024 x 2048: 3.9 against 4.1 the other way),
+    // never for M <= 16 (16 x 512 x 2048: 3.3 against 3.5)
+    else if (m <= kSkinnyMaxM && m > 16 && k <= (m > 64 ? 2048 : m > 32 ? 1024 : 512) && (n + 63) / 64 <= sm_count)
+        kernel = 2 * n128_cols <= sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
+    else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
+    // at most 128 columns: tiles of 256 columns would compute padding for half of their width
+    // (16384 x 4096 x 128: 11.7 us with 128 x 128 tiles against 16.2-16.5 with the 256-wide ones)
+    // one round of 256 x 128 pair tiles is level with or ahead of one round of 128 x 128 tiles (12.6 against 14.0-15.0 us on one box, 11.8 both on another)
+    else if (n <= 128)
+        kernel = 2 * static_cast<long long>((m + 127) / 128) <= sm_count ? B200FP8_KERNEL_CTA1_N64
+                 : (m + 255) / 256 <= sm_count / 2                        ? B200FP8_KERNEL_PAIR_N128
+                                                                               : B200FP8_KERNEL_CTA1_N128;
+    // Long runs are power-limited and the wide tile moves a quarter less data per flop, but it has no second
+    // accumulator slot, so its epilogue (about 5 us) is exposed once per tile: it pays when a tile's main loop
+    // is long.  Measured against the 256 x 256 pair tile: K = 32768 wins 5-8 % from 7 rounds of tiles on
+    // (32768 x 32768 x 2048..8192, 8192 x 32768 x 8192), K = 28672 5 % (8192 x 28672 x 8192; at 3.5 rounds it loses
+    // 7 %), K = 24576 ties, K = 20480 loses; K = 16384 wins 3-8 % at 28 rounds (16384^3), is anywhere between
+    // +3 and -10 % at 14 rounds (16384 x 16384 x 8192, either way round) and loses 4-9 % at 7-10 rounds; K = 8192 loses
+    // 4-15 % everywhere (8192 x 8192 x 28672: 1580 against 1435 us).
+    else if ((k >= 28672 && wide_tiles >= 4LL * (sm_count / 2)) || (k >= 16384 && wide_tiles >= 20LL * (sm_count / 2)))
+        kernel = B200FP8_KERNEL_PAIR_N512;
+    // a short K makes the step a store of C with some arithmetic attached: one-CTA 128 x 256 tiles drain their
+    // accumulators from twice as many independent CTAs as the pairs do (4096 x 512 x 4096: 15.9 against 18.7 us,
+    // 8192 x 512 x 8192: 55 against 75-78, 8192 x 1024 x 8192: 81-84 against 92-93, 2304 x 1024 x 2304: 10.5 against 12.0;
+    // at K = 1536 and 2048 the pair tile leads again)
+    else if (k <= 1024 && n256_tiles >= sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
+    else if (pair_tiles >= sm_count / 2) {
+        kernel = B200FP8_KERNEL_PAIR_N256;
+        // few rounds: count them.  A last round of at most half the pairs costs half a round (it runs as
+        // half-width items); the one-CTA tile is about a tenth slower per round but its rounds hold twice as many
+        // tiles of half the height (1152 x 8192 x 4096: 80 pair tiles = 1.5 rounds, 144 one-CTA tiles = 1: 33.0 against 38.8 us)
+        const long long pairs = sm_count / 2;
+        if (pair_tiles < 4 * pairs) {
+            const long long rem = pair_tiles % pairs;
+            const double rounds_pair = static_cast<double>(pair_tiles / pairs) + (rem == 0 ? 0.0 : 2 * rem <= pairs ? 0.5 : 1.0);
+            const double rounds_single = static_cast<double>((n256_tiles + sm_count - 1) / sm_count);
+            if (1.1 * rounds_single < rounds_pair) kernel = B200FP8_KERNEL_CTA1_N256;
+        }
+    }
+    // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
+    // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
+    else if (4 * pair_tiles >= 3 * (sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N256;
+    // one row of 256 x 128 pair tiles that fills most of the pairs: a quarter less operand traffic per CTA than
+    // 128 x 128 tiles (measured at M = 130..256, N = K = 8192: 5-7 %)
+    else if (m <= 256 && k >= 8192 && 4 * n128_cols >= 3 * (sm_count / 2) && n128_cols <= sm_count / 2)
+        kernel = B200FP8_KERNEL_PAIR_N128;
+    // ... and the same for one or two columns of tiles under a tall A (8192 x 8192 x 136..256: 16.3-17.9 against 17.4-18.7 us)
+    else if (n > 128 && n <= 256 && k >= 8192 && 8LL * ((m + 255) / 256) >= 3 * (sm_count / 2) && 2LL * ((m + 255) / 256) <= sm_count / 2)
+        kernel = B200FP8_KERNEL_PAIR_N128;
+    // one round either way: with K >= 4096 the pair's shared B (32 instead of 48 KiB per CTA and k-block) wins 2-6 %
+    // (640 x 5120 x 5120, 200 x 4096 x 11008, 1024 x 4096 x 4096, 8192 x 8192 x 512); with a shorter K the one-CTA tile does
+    else if (n256_tiles >= sm_count / 2)
+        kernel = (k >= 4096 && 2 * pair_tiles <= sm_count) ? B200FP8_KERNEL_PAIR_N256 : B200FP8_KERNEL_CTA1_N256;
+    // a problem of so few 128 x 128 tiles that twice as many 128 x 64 tiles still fit in one round: half the
+    // main loop and half the epilogue per CTA (1024^3: 6.4 -> 5.5 us, 256^3: 5.2 -> 4.2 us)
+    else if (2 * static_cast<long long>((m + 127) / 128) * n128_cols <= sm_count) kernel = B200FP8_KERNEL_CTA1_N64;
+    else kernel = B200FP8_KERNEL_CTA1_N128;
+    return kernel;
+}
+
 cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b, int b_dtype,
                           long long ldb, float* c, long long ldc, const b200fp8_options* opt, cudaStream_t stream,
                           const PeerSet* peers = nullptr, const Epilogue* epi = nullptr, const EllSpec* ell = nullptr) {
@@ -352,73 +425,7 @@ cudaError_t gemm_dispatch(int m, int k, int n, const void* a, int a_dtype, long 
     cudaError_t e = get_ctx(&ctx);
     if (e != cudaSuccess) return e;
 
-    if (kernel == B200FP8_KERNEL_AUTO) {
-        const long long pair_tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
-        const long long n256_tiles = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
-        const long long wide_tiles = static_cast<long long>((m + 255) / 256) * ((n + 511) / 512);
-        const long long n128_cols = (n + 127) / 128;
-        if (ell) kernel = n256_tiles >= ctx->sm_count / 2 ? B200FP8_KERNEL_CTA1_N256 : B200FP8_KERNEL_CTA1_N128;
-        // M <= 128: the split-K kernel streams a big B from HBM with every SM; with a short K and at most one round of
-        // 128 x 64 tiles there is nothing to split and its reduce-scatter only costs (128 x 2048 x 2048: 12.7 us
-        // against 6.7 us for the tile kernel), so those go to the tile kernels: K <= 2048 for M > 64, K <= 1024 for
-        // 32 < M <= 64 (64 x 2048 x 4096: 5.5 us split in two against 5.9; 64 x 512 x 8192: 3.9 against 5.1 the other way),
-        // K <= 512 for 16 < M <= 32 (32 x 512 x 8192: 3.7 against 4.3; but 32 x 1024 x 2048: 3.9 against 4.1 the other way),
-        // never for M <= 16 (16 x 512 x 2048: 3.3 against 3.5)
-        else if (m <= kSkinnyMaxM && m > 16 && k <= (m > 64 ? 2048 : m > 32 ? 1024 : 512) && (n + 63) / 64 <= ctx->sm_count)
-            kernel = 2 * n128_cols <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64 : B200FP8_KERNEL_CTA1_N128;
-        else if (m <= kSkinnyMaxM) kernel = B200FP8_KERNEL_SKINNY;
-        // at most 128 columns: tiles of 256 columns would compute padding for half of their width
-        // (16384 x 4096 x 128: 11.7 us with 128 x 128 tiles against 16.2-16.5 with the 256-wide ones)
-        // one round of 256 x 128 pair tiles is level with or ahead of one round of 128 x 128 tiles (12.6 against 14.0-15.0 us on one box, 11.8 both on another)
-        else if (n <= 128)
-            kernel = 2 * static_cast<long long>((m + 127) / 128) <= ctx->sm_count ? B200FP8_KERNEL_CTA1_N64
-                     : (m + 255) / 256 <= ctx->sm_count / 2                        ? B200FP8_KERNEL_PAIR_N128
-                                                                                   : B200FP8_KERNEL_CTA1_N128;
-        // Long runs are power-limited and the wide tile moves a quarter less data per flop, but it has no second
-        // accumulator slot, so its epilogue (about 5 us) is exposed once per tile: it pays when a tile's main loop
-        // is long.  Measured against the 256 x 256 pair tile: K = 32768 wins 5-8 % from 7 rounds of tiles on
-        // (32768 x 32768 x 2048..8192, 8192 x 32768 x 8192), K = 28672 5 % (8192 x 28672 x 8192; at 3.5 rounds it loses
-        // 7 %), K = 24576 ties, K = 20480 loses; K = 16384 wins 3 % at 14 rounds (16384 x 16384 x 8192) and loses 4-9 %
-        // at 7-10 rounds; K = 8192 loses 4-15 % everywhere (8192 x 8192 x 28672: 1580 against 1435 us).
-        else if ((k >= 28672 && wide_tiles >= 4LL * (ctx->sm_count / 2)) || (k >= 16384 && wide_tiles >= 13LL * (ctx->sm_count / 2)))
-            kernel = B200FP8_KERNEL_PAIR_N512;
-        // a short K makes the step a store of C with some arithmetic attached: one-CTA 128 x 256 tiles drain their
-        // accumulators from twice as many independent CTAs as the pairs do (4096 x 512 x 4096: 15.9 against 18.7 us,
-        // 8192 x 512 x 8192: 55 against 75-78, 8192 x 1024 x 8192: 81-84 against 92-93, 2304 x 1024 x 2304: 10.5 against 12.0;
-        // at K = 1536 and 2048 the pair tile leads again)
-        else if (k <= 1024 && n256_tiles >= ctx->sm_count / 2) kernel = B200FP8_KERNEL_CTA1_N256;
-        else if (pair_tiles >= ctx->sm_count / 2) {
-            kernel = B200FP8_KERNEL_PAIR_N256;
-            // few rounds: count them.  A last round of at most half the pairs costs half a round (it runs as
-            // half-width items); the one-CTA tile is about a tenth slower per round but its rounds hold twice as many
-            // tiles of half the height (1152 x 8192 x 4096: 80 pair tiles = 1.5 rounds, 144 one-CTA tiles = 1: 33.0 against 38.8 us)
-            const long long pairs = ctx->sm_count / 2;
-            if (pair_tiles < 4 * pairs) {
-                const long long rem = pair_tiles % pairs;
-                const double rounds_pair = static_cast<double>(pair_tiles / pairs) + (rem == 0 ? 0.0 : 2 * rem <= pairs ? 0.5 : 1.0);
-                const double rounds_single = static_cast<double>((n256_tiles + ctx->sm_count - 1) / ctx->sm_count);
-                if (1.1 * rounds_single < rounds_pair) kernel = B200FP8_KERNEL_CTA1_N256;
-            }
-        }
-        // a long K with three quarters of the pairs busy: the pair tile's lower traffic per flop still wins (measured
-        // at M = 300..512, N = K = 8192: 3-8 %); with a short K the one-CTA kernel's smaller tail does
-        else if (4 * pair_tiles >= 3 * (ctx->sm_count / 2) && k >= 8192) kernel = B200FP8_KERNEL_PAIR_N256;
-        // one row of 256 x 128 pair tiles that fills most of the pairs: a quarter less operand traffic per CTA than
-        // 128 x 128 tiles (measured at M = 130..256, N = K = 8192: 5-7 %)
-        else if (m <= 256 && k >= 8192 && 4 * n128_cols >= 3 * (ctx->sm_count / 2) && n128_cols <= ctx->sm_count / 2)
-            kernel = B200FP8_KERNEL_PAIR_N128;
-        // ... and the same for one or two columns of tiles under a tall A (8192 x 8192 x 136..256: 16.3-17.9 against 17.4-18.7 us)
-        else if (n > 128 && n <= 256 && k >= 8192 && 8LL * ((m + 255) / 256) >= 3 * (ctx->sm_count / 2) && 2LL * ((m + 255) / 256) <= ctx->sm_count / 2)
-            kernel = B200FP8_KERNEL_PAIR_N128;
-        // one round either way: with K >= 4096 the pair's shared B (32 instead of 48 KiB per CTA and k-block) wins 2-6 %
-        // (640 x 5120 x 5120, 200 x 4096 x 11008, 1024 x 4096 x 4096, 8192 x 8192 x 512); with a shorter K the one-CTA tile does
-        else if (n256_tiles >= ctx->sm_count / 2)
-            kernel = (k >= 4096 && 2 * pair_tiles <= ctx->sm_count) ? B200FP8_KERNEL_PAIR_N256 : B200FP8_KERNEL_CTA1_N256;
-        // a problem of so few 128 x 128 tiles that twice as many 128 x 64 tiles still fit in one round: half the
-        // main loop and half the epilogue per CTA (1024^3: 6.4 -> 5.5 us, 256^3: 5.2 -> 4.2 us)
-        else if (2 * static_cast<long long>((m + 127) / 128) * n128_cols <= ctx->sm_count) kernel = B200FP8_KERNEL_CTA1_N64;
-        else kernel = B200FP8_KERNEL_CTA1_N128;
-    }
+    if (kernel == B200FP8_KERNEL_AUTO) kernel = choose_kernel(ctx->sm_count, m, k, n, ell != nullptr);
     if ((kernel == B200FP8_KERNEL_SKINNY || kernel == B200FP8_KERNEL_SKINNY_STREAMK) && m > kSkinnyMaxM) return cudaErrorInvalidValue;
     if (ell && kernel != B200FP8_KERNEL_CTA1_N256 && kernel != B200FP8_KERNEL_CTA1_N128 && kernel != B200FP8_KERNEL_CTA1_N64)
         return cudaErrorInvalidValue;
@@ -959,6 +966,12 @@ int b200fp8_ipc_close(void* device_ptr) { return device_ptr ? cudaIpcCloseMemHan
 int b200fp8_ipc_free(void* device_ptr) { return device_ptr ? cudaFree(device_ptr) : cudaSuccess; }
 
 long long b200fp8_launch_count(void) { return t_launches; }
+
+int b200fp8_choose_kernel(int m, int k, int n) {
+    DeviceCtx* ctx = nullptr;
+    if (m <= 0 || n <= 0 || k < 0 || get_ctx(&ctx) != cudaSuccess) return -1;
+    return choose_kernel(ctx->sm_count, m, k, n, false);
+}
 
 int b200fp8_l2_sides(unsigned long long mask[3]) {
     DeviceCtx* ctx = nullptr;

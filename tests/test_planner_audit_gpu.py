@@ -29,8 +29,12 @@ def test_audit_times_auto_and_forced_kernels(tmp_path):
     rows = json.loads(out.read_text())
     assert [(r["m"], r["k"], r["n"]) for r in rows] == [(512, 512, 512), (300, 1024, 3000), (64, 2048, 1024)]
     for r in rows:
-        assert r["auto_us"] > 0 and r["best_us"] > 0 and r["auto_over_best"] == pytest.approx(r["auto_us"] / r["best_us"], rel=0.02)
+        assert r["auto_us"] > 0 and r["best_us"] > 0 and r["chosen_over_best"] == pytest.approx(r["chosen_us"] / r["best_us"], rel=0.02)
+        assert str(r["chosen_kernel"]) in r["us_by_kernel"]
         assert set(r["us_by_kernel"]) >= {"1", "2", "3", "6", "7"}
     assert set(rows[2]["us_by_kernel"]) >= {"4", "8"}          # M <= 128: the split-K kernels are timed too
+    lib = load_package()._cabi.lib()
+    assert lib.b200fp8_choose_kernel(16, 8192, 8192) == 4 and lib.b200fp8_choose_kernel(8192, 8192, 8192) == 3
+    assert lib.b200fp8_choose_kernel(0, 64, 64) == -1
     # an impossible threshold flags every shape and turns the exit code
     assert tool.main(["512x512x512", "--threshold", "0.01"], pkg=load_package()) == 1
