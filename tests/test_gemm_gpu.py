@@ -524,3 +524,49 @@ def test_reference_driver_links_and_verifies():
         assert line, res.stdout
         assert float(line[0].split()[-1]) < 1e-3, res.stdout
         assert "There are 0 errors." in res.stdout
+
+
+# One shape for every branch of the automatic kernel choice (the id it must land on, asked through
+# b200fp8_choose_kernel, guards the list against a rule that silently stops being reached).
+PLANNER_BRANCHES = [
+    ((1152, 1024, 4096), 1),     # K <= 1024: one-CTA 128 x 256 tiles
+    ((4096, 512, 4096), 1),
+    ((1152, 8192, 4096), 1),     # 1.5 rounds of pair tiles against one round of one-CTA tiles
+    ((16384, 256, 128), 6),      # N <= 128 under a tall A: one round of 256 x 128 pair tiles
+    ((4096, 1024, 96), 7),       # N <= 128, few row tiles: 128 x 64 tiles
+    ((40000, 256, 128), 2),      # N <= 128, more row tiles than pairs: 128 x 128 tiles
+    ((8192, 8192, 136), 6),      # two columns of tiles under a tall A, long K
+    ((640, 4096, 5120), 3),      # one round either way, K >= 4096: pair tiles
+    ((200, 4096, 11008), 3),
+    ((2048, 2048, 2048), 1),     # one round, short K: one-CTA tiles
+    ((256, 8192, 8192), 6),      # one row of 256 x 128 pair tiles
+    ((8192, 28672, 8192), 5),    # long K, seven rounds of wide tiles
+    ((4096, 28672, 4096), 3),    # long K but two rounds: pair tiles
+    ((48, 2048, 2048), 4),       # M <= 64 with K = 2048: split-K
+    ((96, 2048, 4096), 7),       # M > 64 with K <= 2048: tile kernel
+    ((64, 1024, 8192), 7),       # 32 < M <= 64 with K <= 1024: tile kernel
+    ((32, 512, 8192), 7),        # 16 < M <= 32 with K <= 512: tile kernel
+    ((32, 1024, 2048), 4),
+    ((16, 512, 2048), 4),        # M <= 16: always split-K
+    ((128, 4096, 1024), 4),      # eight N tiles: splits capped by the k-blocks each would own
+]
+
+
+@pytest.mark.parametrize("shape,expected", PLANNER_BRANCHES)
+def test_every_planner_branch_selects_its_kernel_and_computes_the_product(g, oracle, shape, expected):
+    from __graft_entry__ import load_package
+    m, k, n = shape
+    lib = load_package()._cabi.lib()
+    assert lib.b200fp8_choose_kernel(m, k, n) == expected
+    a, b = random_operands(g, m, k, n, 0, 1, seed=0xB200F800 + 300 + expected)
+    out = run(g, a, b, m, k, n)
+    if m * n <= 1 << 22 and m * n * k <= 1 << 33:
+        assert_within_tolerance(oracle, out.cpu().numpy(), host_bytes(a), 0, host_bytes(b), 1)
+    else:
+        sampled_check(oracle, a, b, out, 0, 1, rows=8, cols=8, points=4096)
+    assert freivalds(a, b, out) <= 1.0
+    # and the forced kernel gives the same bits as the automatic call: the choice is only a choice
+    forced = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    g.gemm_ex(a, b, forced, kernel=expected)
+    torch.cuda.synchronize()
+    assert torch.equal(forced, out)
