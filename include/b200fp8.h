@@ -149,8 +149,10 @@ typedef struct b200fp8_epilogue {
    both by short branch-free FP32 formulas: within 2e-6 relative of the exact function for t >= 0 and within
    1e-6 |t| absolute for t < 0 (where the exact value itself falls below that). */
 enum { B200FP8_ACT_NONE = 0, B200FP8_ACT_RELU = 1, B200FP8_ACT_GELU_ERF = 2, B200FP8_ACT_GELU_TANH = 3 };
-/* size of b200fp8_epilogue before `activation` was added (offset of that field) */
-#define B200FP8_EPILOGUE_V1_BYTES ((int)offsetof(b200fp8_epilogue, activation))
+/* sizeof(b200fp8_epilogue) before `activation` was added: the struct then ended with bias_dtype and its tail padding,
+   where `activation` now sits */
+#define B200FP8_EPILOGUE_V1_BYTES \
+    ((int)((offsetof(b200fp8_epilogue, activation) + sizeof(void*) - 1) / sizeof(void*) * sizeof(void*)))
 
 int b200fp8_gemm_rowcol_epilogue(int m, int k, int n, const void* a, int a_dtype, long long lda, const void* b,
                                  int b_dtype, long long ldb, void* d, int d_dtype, long long ldd,

@@ -295,7 +295,10 @@ def test_shorter_epilogue_struct_of_older_callers_is_accepted(g):
     want = torch.empty((m, n), dtype=torch.float32, device="cuda")
     g.gemm_epilogue(a, b, want, alpha=0.5, kernel=3)
     ep = pkg._cabi.EpilogueDesc()
-    ep.struct_bytes = pkg._cabi.EpilogueDesc.activation.offset
+    class OldEpilogue(ctypes.Structure):                  # the struct as older callers were compiled against it
+        _fields_ = pkg._cabi.EpilogueDesc._fields_[:9]
+    assert OldEpilogue._fields_[-1][0] == "bias_dtype" and ctypes.sizeof(OldEpilogue) == 64
+    ep.struct_bytes = ctypes.sizeof(OldEpilogue)
     ep.alpha, ep.beta = 0.5, 0.0
     wrong_m = torch.full((m,), 1000.0, device="cuda")
     wrong_n = torch.full((n,), 1000.0, device="cuda")
