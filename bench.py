@@ -1003,7 +1003,7 @@ def main() -> int:
             runner = shard_mod.HostShardedGemm(M, K, sh, fa, fb, dev)
             call = lambda **kw: runner(ha, hb, hc, depth=args.depth, kernel=args.kernel, **kw)
             api = ("shard.HostShardedGemm (upload M/N rows of A and the B shard; rows of A broadcast rank by rank over NVLink; "
-                   "operator in row blocks as the rows arrive; download of C overlapped), wall clock, max over ranks")
+                   "the own rows against the B shard piece by piece as it lands, the other row blocks as their rows arrive; download of C overlapped), wall clock, max over ranks")
             h2d = rows * K + n_local * K
         else:
             ha = torch.empty((M, K), dtype=torch.uint8).pin_memory().view(fa)

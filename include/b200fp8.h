@@ -269,6 +269,16 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
 int b200fp8_host_release(void);
 
 /*
+ * A pitched copy, enqueued on `stream`: `rows` rows of `width_bytes` bytes from `src` (row pitch `src_pitch` bytes) to
+ * `dst` (row pitch `dst_pitch`), between device memory and pinned host memory in either direction (cudaMemcpy2DAsync
+ * with the direction taken from the pointers).  What the host-pointer entry above uses for its blocks of C; exported
+ * for callers that pipeline column blocks of a row-major matrix themselves (the multi-GPU host driver does).
+ * No counterpart in the reference.
+ */
+int b200fp8_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                          void* stream);
+
+/*
  * Thread safety.  Every entry point may be called from several host threads at once, on the
  * same or on different devices.  Calls of b200fp8_gemm_rowcol_f32_host on ONE device are
  * serialised inside the library (they share that device's staging buffers and copy streams);

@@ -54,6 +54,7 @@ DECLARED_SYMBOLS = (
     "b200fp8_ipc_close",
     "b200fp8_ipc_free",
     "b200fp8_launch_count",
+    "b200fp8_copy_2d_async",
     "b200fp8_l2_sides",
     "b200fp8_choose_kernel",
     "b200fp8_version",
@@ -127,6 +128,7 @@ def lib() -> ctypes.CDLL:
         L.b200fp8_multi_run.argtypes = [vp, ci, ctypes.POINTER(Options), ctypes.POINTER(ctypes.c_float)]
         L.b200fp8_multi_download.argtypes = [vp, vp, ci]
         L.b200fp8_host_release.argtypes = []
+        L.b200fp8_copy_2d_async.argtypes = [vp, ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, vp]
         L.b200fp8_enable_peer_access.argtypes = [ci]
         L.b200fp8_ipc_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(vp), ctypes.c_char_p]
         L.b200fp8_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]

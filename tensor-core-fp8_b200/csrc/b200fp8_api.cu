@@ -746,6 +746,13 @@ int b200fp8_gemm_rowcol_f32_host(int m, int k, int n, const void* a_host, int a_
     return first;
 }
 
+int b200fp8_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                          void* stream) {
+    if (rows == 0 || width_bytes == 0) return cudaSuccess;
+    if (!dst || !src || dst_pitch < width_bytes || src_pitch < width_bytes) return cudaErrorInvalidValue;
+    return cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault, static_cast<cudaStream_t>(stream));
+}
+
 int b200fp8_host_release(void) {
     DeviceCtx* ctx = nullptr;
     cudaError_t e = get_ctx(&ctx);

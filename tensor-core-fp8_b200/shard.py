@@ -173,13 +173,16 @@ class HostShardedGemm:
     NVLink.  The phases overlap: uploads run on a copy stream; rank j's rows travel as broadcast j on a
     communication stream; the operator runs in row blocks, the own block first (it needs no communication) and
     block j as soon as broadcast j has landed; each finished block of C goes down on a third stream while the next
-    block computes.  `__call__(a_rows_host, b_shard_host, c_shard_host)`: pinned host tensors holding this rank's M/R
+    block computes.  The own rows do not wait for the whole B shard either: B goes up in `col_blocks` pieces and the
+    own rows are multiplied with each piece as it lands, the finished column block of C leaving at once (a pitched
+    copy), so that the download -- which bounds the call -- starts after a fraction of the uploads.  `__call__(a_rows_host, b_shard_host, c_shard_host)`: pinned host tensors holding this rank's M/R
     rows of A, its rows of B and room for its M x n column block of C; returns when the block is complete in host
     memory.  With `breakdown=True` it also returns the milliseconds, from the call's start, at which each phase
     ended on the device.
     """
 
-    def __init__(self, m: int, k: int, shard: Shard, a_dtype, b_dtype, device, group=None, row_blocks: int = 8):
+    def __init__(self, m: int, k: int, shard: Shard, a_dtype, b_dtype, device, group=None, row_blocks: int = 8,
+                 col_blocks: int = 4):
         import torch
         import torch.distributed as dist
         self.group = group
@@ -197,6 +200,10 @@ class HostShardedGemm:
         step = -(-step // 256) * 256
         self.blocks = {j: [(j * self.rows_own + r0, min((j + 1) * self.rows_own, j * self.rows_own + r0 + step))
                            for r0 in range(0, self.rows_own, step)] for j in range(self.world)}
+        # column pieces of the B shard for the own rows (multiples of 256 columns; one piece if the shard is narrow)
+        cstep = -(-shard.n // max(1, col_blocks))
+        cstep = max(256, -(-cstep // 256) * 256)
+        self.col_pieces = [(c0, min(shard.n, c0 + cstep)) for c0 in range(0, shard.n, cstep)]
         self.copy_in = torch.cuda.Stream(device=self.device)
         self.comm = torch.cuda.Stream(device=self.device)
         self.copy_out = torch.cuda.Stream(device=self.device)
@@ -212,10 +219,14 @@ class HostShardedGemm:
         r0 = self.rank * self.rows_own
         own = self.a[r0:r0 + self.rows_own]
         self.copy_in.wait_stream(cur)
+        piece_up = []
         with torch.cuda.stream(self.copy_in):
             own.view(torch.uint8).copy_(a_rows_host.view(torch.uint8), non_blocking=True)
             up_a.record(self.copy_in)
-            self.b.view(torch.uint8).copy_(b_shard_host.view(torch.uint8), non_blocking=True)
+            for (c0, c1) in self.col_pieces:             # rows c0..c1 of the shard = columns c0..c1 of this rank's C
+                self.b[c0:c1].view(torch.uint8).copy_(b_shard_host[c0:c1].view(torch.uint8), non_blocking=True)
+                piece_up.append(torch.cuda.Event())
+                piece_up[-1].record(self.copy_in)
             up_b.record(self.copy_in)
         arrived = {}
         if self.world > 1:
@@ -231,19 +242,33 @@ class HostShardedGemm:
         else:
             last_bcast.record(cur)
         cur.wait_event(up_a)
-        cur.wait_event(up_b)
-        order = [self.rank] + [j for j in range(self.world) if j != self.rank]
         first = True
-        for j in order:
-            if j != self.rank:
-                cur.wait_event(arrived[j])
-            for (lo, hi) in self.blocks[j]:
-                g.gemm_ex(self.a[lo:hi], self.b, self.c[lo:hi], depth=depth, kernel=kernel)
+        from . import _cabi
+        lib = _cabi.lib()
+        n = self.shard.n
+        # own rows: column piece by column piece, each as soon as its rows of B are on the device
+        for p, (c0, c1) in enumerate(self.col_pieces):
+            cur.wait_event(piece_up[p])
+            for (lo, hi) in self.blocks[self.rank]:
+                g.gemm_ex(self.a[lo:hi], self.b[c0:c1], self.c[lo:hi, c0:c1], depth=depth, kernel=kernel)
                 done = torch.cuda.Event()
                 done.record(cur)
                 if first:
                     first_gemm.record(cur)
                     first = False
+                self.copy_out.wait_event(done)
+                dst = c_shard_host.data_ptr() + (lo * n + c0) * 4
+                src = self.c.data_ptr() + (lo * n + c0) * 4
+                with torch.cuda.device(self.device):
+                    _cabi.check(lib.b200fp8_copy_2d_async(dst, n * 4, src, n * 4, (c1 - c0) * 4, hi - lo,
+                                                          self.copy_out.cuda_stream), "copy_2d_async")
+        # the other ranks' rows: the whole shard is up by now (the last piece's event has been waited for)
+        for j in (j for j in range(self.world) if j != self.rank):
+            cur.wait_event(arrived[j])
+            for (lo, hi) in self.blocks[j]:
+                g.gemm_ex(self.a[lo:hi], self.b, self.c[lo:hi], depth=depth, kernel=kernel)
+                done = torch.cuda.Event()
+                done.record(cur)
                 self.copy_out.wait_event(done)
                 with torch.cuda.stream(self.copy_out):
                     c_shard_host[lo:hi].copy_(self.c[lo:hi], non_blocking=True)
