@@ -1000,7 +1000,7 @@ def main() -> int:
             rows = M // world
             ha = torch.empty((rows, K), dtype=torch.uint8).pin_memory().view(fa)
             ha.view(torch.uint8).copy_(a[rank * rows:(rank + 1) * rows].view(torch.uint8))
-            runner = shard_mod.HostShardedGemm(M, K, sh, fa, fb, dev)
+            runner = shard_mod.HostShardedGemm(M, K, sh, fa, fb, dev, col_blocks=int(os.environ.get("B200FP8_E2E_COL_BLOCKS", "4")))
             call = lambda **kw: runner(ha, hb, hc, depth=args.depth, kernel=args.kernel, **kw)
             api = ("shard.HostShardedGemm (upload M/N rows of A and the B shard; rows of A broadcast rank by rank over NVLink; "
                    "the own rows against the B shard piece by piece as it lands, the other row blocks as their rows arrive; download of C overlapped), wall clock, max over ranks")
